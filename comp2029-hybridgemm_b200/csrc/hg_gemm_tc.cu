@@ -1,0 +1,715 @@
+// Hybrid MXFP4xMXFP8 + MXFP8xMXFP8 output-channel GEMM for sm_100a.
+//
+// One persistent launch covers BOTH precision partitions of a hybrid linear
+// (the reference runs two CUTLASS SM120 kernels on two streams,
+// integrations/vllm/native/runtime.cu:31-43, or a single-kernel precision
+// switch, src/kernel/output_channel_switch_collective.cuh:146-172):
+//
+//   out[t, ids[r]] = sum_g 2^(sw[r,g]+sx[t,g]-254) * sum_{k in g} W[r,k] * X[t,k]
+//
+// * MMA shape: tcgen05.mma kind::mxf8f6f4.block_scale, M = 128 weight rows,
+//   N = n_tile tokens (16..128), K = 32 per instruction, fp32 accumulators in
+//   TMEM.  The A format (E2M1 or E4M3), the tensor map and the expected TMA
+//   byte count are chosen per tile, so low and high tiles share one pipeline.
+// * Operands: TMA (cp.async.bulk.tensor, 128B swizzle) into a ring of K128
+//   stages.  Packed E2M1 rows are expanded to the 8-bit container the f8f6f4
+//   kinds want by the tensor map type 16U4_ALIGN16B: 0.5 B/element from HBM,
+//   1 B/element in shared memory.
+// * Scales: the 512-byte atoms (128 rows x 4 K32 groups) travel by 1-D bulk
+//   copies and go to TMEM with tcgen05.cp 32x128b.warpx4; the byte of the
+//   current K32 block is selected with the a_sf_id/b_sf_id descriptor fields.
+// * Schedule: a host-built list of work units (row tile, token tile, K range)
+//   per CTA: data-parallel, split-K or stream-K.  Tiles cut along K write fp32
+//   partials to a workspace; the LAST unit to arrive (atomic ticket, no
+//   spinning) sums the partials in K order, so the result is deterministic.
+// * Epilogue: tcgen05.ld 32x32b, fp32 -> bf16/fp16 (RNE), scattered straight to
+//   out[t*N + ids[r]]; consecutive lanes own consecutive rows, so sorted maps
+//   give contiguous 64-byte runs.  Two accumulator buffers let the epilogue of
+//   one unit overlap the main loop of the next.
+// * Every mbarrier wait is bounded (wall-clock); on expiry the CTA records a
+//   code in the status word, lets copies in flight land, frees TMEM and exits.
+#include <cuda.h>
+
+#include <algorithm>
+#include <cstring>
+#include <memory>
+#include <mutex>
+
+#include "hg_gemm_tc.cuh"
+
+namespace hg {
+
+// ---------------------------------------------------------------------------------------------
+// Device side
+// ---------------------------------------------------------------------------------------------
+
+struct TcParams {
+  int rows[2];
+  int tiles[2];
+  const uint8_t* sfa[2];
+  const int32_t* ids[2];
+  const uint8_t* sfb;
+  uint16_t* out;
+  int outputs, tokens, k, kblocks;
+  int n_tile, stages, dtype;
+  uint32_t tmem_cols;
+  const WorkUnit* units;
+  const int* cta_begin;
+  float* workspace;
+  int* counters;
+  int* status;
+};
+
+enum : int { kErrProducer = 1, kErrMmaFull = 2, kErrMmaAcc = 3, kErrEpilogue = 4, kErrDrain = 5 };
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ unsigned long long global_timer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait.  Returns false when the limit expired or another role of this
+// CTA already gave up (abort flag in shared memory).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long start = global_timer();
+  for (uint32_t spin = 1;; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & 63u) == 0) {
+      if (*abort_flag) return false;
+      if (global_timer() - start > kWaitLimitNs) return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_cp_scales(uint32_t tmem_addr, uint64_t smem_desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(smem_desc) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                       uint32_t accumulate, uint32_t tmem_sfa, uint32_t tmem_sfb) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n"
+      "}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+      : "memory");
+}
+__device__ __forceinline__ void tc_load8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr));
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (tcgen05 format, version 1).
+//   bits [0,14) start address >> 4, [16,30) leading byte offset >> 4,
+//   [32,46) stride byte offset >> 4, [46,48) version = 1, [61,64) swizzle mode.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo, uint32_t layout) {
+  return uint64_t((addr & 0x3ffffu) >> 4) | (uint64_t(lbo >> 4) << 16) | (uint64_t(sbo >> 4) << 32) |
+         (uint64_t(1) << 46) | (uint64_t(layout) << 61);
+}
+constexpr uint32_t kSwizzle128B = 2, kSwizzleNone = 0;
+
+// Instruction descriptor of kind::mxf8f6f4.block_scale:
+//   [4,6) B scale id, [7,10) A format (0 E4M3, 5 E2M1), [10,13) B format, [15] A major, [16] B major
+//   (0 = K-major), [17,23) N>>3, [23] scale format (1 = UE8M0), [24,29) M>>4, [29,31) A scale id.
+__device__ __forceinline__ uint32_t instr_desc(bool a_is_fp4, int n_tile) {
+  return (a_is_fp4 ? 5u << 7 : 0u) | (0u << 10) | (uint32_t(n_tile >> 3) << 17) | (1u << 23) |
+         (uint32_t(kTileRows >> 4) << 24);
+}
+
+__device__ __forceinline__ bool epilogue_all(bool ok) {
+  uint32_t r;
+  asm volatile(
+      "{\n"
+      ".reg .pred p, q;\n"
+      "setp.ne.b32 p, %1, 0;\n"
+      "barrier.cta.red.and.pred q, 1, 128, p;\n"
+      "selp.u32 %0, 1, 0, q;\n"
+      "}"
+      : "=r"(r)
+      : "r"(uint32_t(ok))
+      : "memory");
+  return r != 0;
+}
+__device__ __forceinline__ void epilogue_sync() { asm volatile("barrier.cta.sync 1, 128;" ::: "memory"); }
+
+template <typename T>
+__device__ __forceinline__ void scatter_store(uint16_t* out, int64_t index, float v) {
+  out[index] = from_float<T>(v);
+}
+
+struct SmemLayout {
+  uint32_t a, b, sfa, sfb, bars;  // byte offsets from the 1024-aligned base
+  uint32_t b_stage;
+};
+__host__ __device__ inline SmemLayout smem_layout(int stages, int n_tile) {
+  SmemLayout s;
+  s.b_stage = uint32_t(n_tile) * 128u;
+  s.a = 0;
+  s.b = s.a + uint32_t(stages) * 16384u;
+  s.sfa = s.b + uint32_t(stages) * s.b_stage;
+  s.sfb = s.sfa + uint32_t(stages) * 512u;
+  s.bars = s.sfb + uint32_t(stages) * 512u;
+  return s;
+}
+constexpr int kBarrierBytes = (2 * kMaxStages + 5) * 8 + 32;
+
+template <typename T>
+__global__ void __launch_bounds__(kTcThreads, 1)
+hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant__ CUtensorMap map_low,
+                      const __grid_constant__ CUtensorMap map_high, const __grid_constant__ CUtensorMap map_act) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const SmemLayout lay = smem_layout(p.stages, p.n_tile);
+
+  // Barrier block: full[stages], empty[stages], acc_full[2], acc_empty[2], drain, then three words.
+  const uint32_t bars = base + lay.bars;
+  auto full_bar = [&](int s) { return bars + uint32_t(s) * 8u; };
+  auto empty_bar = [&](int s) { return bars + uint32_t(p.stages + s) * 8u; };
+  auto acc_full_bar = [&](int s) { return bars + uint32_t(2 * p.stages + s) * 8u; };
+  auto acc_empty_bar = [&](int s) { return bars + uint32_t(2 * p.stages + 2 + s) * 8u; };
+  const uint32_t drain_bar = bars + uint32_t(2 * p.stages + 4) * 8u;
+  volatile int* words = reinterpret_cast<volatile int*>(base_ptr + lay.bars + (2 * p.stages + 5) * 8);
+  volatile int* tmem_slot = words;       // TMEM base address written by tcgen05.alloc
+  volatile int* abort_flag = words + 1;  // set by the first role whose wait expired
+  volatile int* ticket_slot = words + 2; // split-K arrival ticket broadcast
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(acc_full_bar(s), 1);
+      mbar_init(acc_empty_bar(s), 4);
+    }
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    *ticket_slot = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(const_cast<int*>(tmem_slot))), "r"(p.tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = uint32_t(*tmem_slot);
+
+  // TMEM columns: two accumulators, then two sets of (SFA, SFB), 4 columns each.
+  const uint32_t acc_stride = uint32_t((p.n_tile + 31) & ~31);
+  const uint32_t sf_cols = tmem_base + 2 * acc_stride;
+
+  const int unit_begin = p.cta_begin[blockIdx.x], unit_end = p.cta_begin[blockIdx.x + 1];
+  int error = 0;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      const uint32_t tx_common = lay.b_stage + 1024u;
+      for (int u = unit_begin; u < unit_end && !error; ++u) {
+        const WorkUnit wu = p.units[u];
+        const int part = wu.tile >= p.tiles[0];
+        const int tile = part ? wu.tile - p.tiles[0] : wu.tile;
+        const CUtensorMap* map_w = part ? &map_high : &map_low;
+        const uint32_t tx = tx_common + (part ? 16384u : 8192u);
+        const int token0 = wu.token_tile * p.n_tile;
+        const uint8_t* sfa_src = p.sfa[part] + (int64_t(tile) * p.kblocks) * 512;
+        const uint8_t* sfb_src = p.sfb + (int64_t(token0 / 128) * p.kblocks) * 512;
+        for (int kb = wu.kb_begin; kb < wu.kb_end; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { error = kErrProducer; break; }
+          const uint32_t bar = full_bar(stage);
+          mbar_expect_tx(bar, tx);
+          tma_load_2d(base + lay.a + uint32_t(stage) * 16384u, map_w, bar, kb * kTileK, tile * kTileRows);
+          tma_load_2d(base + lay.b + uint32_t(stage) * lay.b_stage, &map_act, bar, kb * kTileK, token0);
+          bulk_load(base + lay.sfa + uint32_t(stage) * 512u, sfa_src + int64_t(kb) * 512, 512u, bar);
+          bulk_load(base + lay.sfb + uint32_t(stage) * 512u, sfb_src + int64_t(kb) * 512, 512u, bar);
+          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0, kiter = 0, issued = 0;
+      int acc_it = 0;
+      // SFB of token tile t0 sits in column (t0 % 128) / 32 of its 128-token atom.
+      for (int u = unit_begin; u < unit_end && !error; ++u, ++acc_it) {
+        const WorkUnit wu = p.units[u];
+        const int part = wu.tile >= p.tiles[0];
+        const int slot = acc_it & 1;
+        if (!mbar_wait(acc_empty_bar(slot), (uint32_t(acc_it >> 1) & 1u) ^ 1u, abort_flag)) { error = kErrMmaAcc; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + uint32_t(slot) * acc_stride;
+        const uint32_t idesc = instr_desc(part == 0, p.n_tile);
+        const uint32_t sfb_col = uint32_t((wu.token_tile * p.n_tile) % 128) / 32u;
+        for (int kb = wu.kb_begin; kb < wu.kb_end; ++kb, ++kiter) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag)) { error = kErrMmaFull; break; }
+          tc_fence_after();
+          const uint32_t sf_set = sf_cols + (kiter & 1u) * 8u;
+          tc_cp_scales(sf_set, smem_desc(base + lay.sfa + uint32_t(stage) * 512u, 0, 128, kSwizzleNone));
+          tc_cp_scales(sf_set + 4, smem_desc(base + lay.sfb + uint32_t(stage) * 512u, 0, 128, kSwizzleNone));
+          const uint64_t desc_a = smem_desc(base + lay.a + uint32_t(stage) * 16384u, 0, 1024, kSwizzle128B);
+          const uint64_t desc_b = smem_desc(base + lay.b + uint32_t(stage) * lay.b_stage, 0, 1024, kSwizzle128B);
+#pragma unroll
+          for (uint32_t j = 0; j < 4; ++j) {
+            // 32 K-elements = 32 bytes further along the swizzled row: start address field += 2.
+            tc_mma(tmem_d, desc_a + 2 * j, desc_b + 2 * j, idesc | (j << 29) | (j << 4),
+                   (kb > wu.kb_begin || j > 0) ? 1u : 0u, sf_set, sf_set + 4 + sfb_col);
+          }
+          tc_commit(empty_bar(stage));
+          ++issued;
+          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+        }
+        if (!error) tc_commit(acc_full_bar(slot));
+      }
+      // Let every MMA issued by this thread retire before TMEM is released.
+      tc_commit(drain_bar);
+      if (!mbar_wait(drain_bar, 0, abort_flag) && !error) error = kErrDrain;
+      if (issued) atomicAdd(p.status + 1, int(issued));
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;                 // TMEM lanes this warp may read
+    const int row_in_tile = quarter * 32 + lane;
+    const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
+    int acc_it = 0, stored = 0;
+    for (int u = unit_begin; u < unit_end; ++u, ++acc_it) {
+      const WorkUnit wu = p.units[u];
+      const int part = wu.tile >= p.tiles[0];
+      const int tile = part ? wu.tile - p.tiles[0] : wu.tile;
+      const int slot = acc_it & 1;
+      const bool ok = mbar_wait(acc_full_bar(slot), uint32_t(acc_it >> 1) & 1u, abort_flag);
+      if (!epilogue_all(ok)) { error = kErrEpilogue; break; }
+      tc_fence_after();
+      const int row = tile * kTileRows + row_in_tile;
+      const bool row_ok = row < p.rows[part];
+      const int channel = row_ok ? p.ids[part][row] : 0;
+      const int token0 = wu.token_tile * p.n_tile;
+      const uint32_t taddr = tmem_base + lane_addr + uint32_t(slot) * acc_stride;
+      float* ws = wu.nsplit > 1
+                      ? p.workspace + (int64_t(wu.ws_slot) + wu.split) * (int64_t(p.n_tile) * kTileRows) + row_in_tile
+                      : nullptr;
+      for (int c0 = 0; c0 < p.n_tile; c0 += 8) {
+        uint32_t r[8];
+        tc_load8(taddr + uint32_t(c0), r);
+        tc_wait_ld();
+        if (ws) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) ws[int64_t(c0 + i) * kTileRows] = __uint_as_float(r[i]);
+        } else if (row_ok) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int token = token0 + c0 + i;
+            if (token < p.tokens) scatter_store<T>(p.out, int64_t(token) * p.outputs + channel, __uint_as_float(r[i]));
+          }
+        }
+      }
+      // Accumulator buffer may be overwritten by the next-but-one unit.
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty_bar(slot));
+
+      if (wu.nsplit > 1) {
+        // Deterministic split-K fix-up: the last unit of the tile to arrive sums
+        // all partials in K order.  No unit ever waits for another.
+        __threadfence();
+        epilogue_sync();
+        if (threadIdx.x == 64) *ticket_slot = atomicAdd(p.counters + wu.counter, 1);
+        epilogue_sync();
+        const int ticket = *ticket_slot;
+        if (ticket == wu.nsplit - 1) {
+          __threadfence();
+          const float* src = p.workspace + int64_t(wu.ws_slot) * (int64_t(p.n_tile) * kTileRows) + row_in_tile;
+          if (row_ok) {
+            for (int c = 0; c < p.n_tile; ++c) {
+              const int token = token0 + c;
+              if (token >= p.tokens) break;
+              float sum = 0.f;
+              for (int s = 0; s < wu.nsplit; ++s)
+                sum += __ldcg(src + (int64_t(s) * p.n_tile + c) * kTileRows);
+              scatter_store<T>(p.out, int64_t(token) * p.outputs + channel, sum);
+            }
+          }
+          if (threadIdx.x == 64) p.counters[wu.counter] = 0;  // ready for the next launch
+        }
+        epilogue_sync();  // ticket_slot is reused by the next unit
+      }
+      ++stored;
+    }
+    if (threadIdx.x == 64 && stored) atomicAdd(p.status + 2, stored);
+  }
+
+  if (error) {
+    *abort_flag = 1;
+    atomicCAS(p.status, 0, error * 1000000 + int(blockIdx.x));
+    // Give copies and MMAs in flight time to land before shared memory and TMEM are released.
+    const unsigned long long start = global_timer();
+    while (global_timer() - start < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side: schedule
+// ---------------------------------------------------------------------------------------------
+
+static int round_up(int v, int m) { return (v + m - 1) / m * m; }
+
+Plan make_plan(int rows_low, int rows_high, int tokens, int k, int sms, int schedule) {
+  Plan plan;
+  const int tiles_low = (rows_low + kTileRows - 1) / kTileRows, tiles_high = (rows_high + kTileRows - 1) / kTileRows;
+  const int tiles = tiles_low + tiles_high, kblocks = k / kTileK;
+  plan.n_tile = tokens >= 128 ? 128 : std::max(16, round_up(tokens, 16));
+  plan.token_tiles = (tokens + plan.n_tile - 1) / plan.n_tile;
+  const int stage_bytes = 16384 + plan.n_tile * 128 + 1024;
+  plan.stages = std::min(kMaxStages, (232448 - 1024 - kBarrierBytes) / stage_bytes);
+  plan.smem_bytes = 1024 + plan.stages * stage_bytes + kBarrierBytes;
+  int cols = 2 * round_up(plan.n_tile, 32) + 16, pow2 = 32;
+  while (pow2 < cols) pow2 *= 2;
+  plan.tmem_cols = pow2;
+
+  // Cost of one K128 block of a tile in HBM bytes (weights dominate): E2M1 8 KiB, E4M3 16 KiB.
+  auto weight = [&](int tile) { return tile < tiles_low ? 1 : 2; };
+  const int items = tiles * plan.token_tiles;
+  int64_t total_cost = 0;
+  for (int t = 0; t < tiles; ++t) total_cost += int64_t(weight(t)) * kblocks * plan.token_tiles;
+  plan.grid = int(std::min<int64_t>(sms, std::max<int64_t>(1, items)));
+
+  auto greedy = [&](std::vector<WorkUnit> units, std::vector<int64_t> cost) {
+    // Longest-processing-time assignment of whole units to CTAs.
+    std::vector<int> order(units.size());
+    for (size_t i = 0; i < order.size(); ++i) order[i] = int(i);
+    std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return cost[a] > cost[b]; });
+    const int grid = int(std::min<size_t>(size_t(sms), std::max<size_t>(1, units.size())));
+    std::vector<std::vector<int>> per(grid);
+    std::vector<int64_t> load(grid, 0);
+    for (int i : order) {
+      int best = int(std::min_element(load.begin(), load.end()) - load.begin());
+      per[best].push_back(i);
+      load[best] += cost[i];
+    }
+    plan.grid = grid;
+    plan.units.clear();
+    plan.cta_begin.assign(1, 0);
+    for (auto& list : per) {
+      std::sort(list.begin(), list.end());
+      for (int i : list) plan.units.push_back(units[i]);
+      plan.cta_begin.push_back(int(plan.units.size()));
+    }
+    return *std::max_element(load.begin(), load.end());
+  };
+
+  // Data-parallel candidate.
+  std::vector<WorkUnit> dp;
+  std::vector<int64_t> dp_cost;
+  for (int t = 0; t < tiles; ++t)
+    for (int tt = 0; tt < plan.token_tiles; ++tt) {
+      dp.push_back(WorkUnit{t, tt, 0, kblocks, 0, 1, 0, 0});
+      dp_cost.push_back(int64_t(weight(t)) * kblocks);
+    }
+
+  auto split_k = [&](int splits) {
+    std::vector<WorkUnit> units;
+    std::vector<int64_t> cost;
+    int slots = 0, counters = 0;
+    for (int t = 0; t < tiles; ++t)
+      for (int tt = 0; tt < plan.token_tiles; ++tt) {
+        const int s_tile = std::min(splits * weight(t), kblocks);
+        for (int s = 0; s < s_tile; ++s) {
+          const int b = int(int64_t(kblocks) * s / s_tile), e = int(int64_t(kblocks) * (s + 1) / s_tile);
+          units.push_back(WorkUnit{t, tt, b, e, s, s_tile, slots, counters});
+          cost.push_back(int64_t(weight(t)) * (e - b));
+        }
+        if (s_tile > 1) { slots += s_tile; ++counters; }
+        else units.back().nsplit = 1;
+      }
+    plan.ws_slots = slots;
+    plan.counters = counters;
+    return greedy(units, cost);
+  };
+
+  auto stream_k = [&]() {
+    // Equal share of cost per CTA.  The ideal cut points (in cost units) are mapped
+    // to (item, K128 block) positions and snapped to the item boundary when they
+    // would leave a piece shorter than kMinBlocks (short pieces only add fix-up
+    // traffic), so every CTA's load is within about one block of the ideal share.
+    const int kMinBlocks = 2;
+    plan.grid = int(std::max<int64_t>(1, std::min<int64_t>(sms, total_cost / (2 * kMinBlocks))));
+    std::vector<int64_t> start(items + 1, 0);   // cumulative cost at the start of each (tile, token tile)
+    for (int i = 0; i < items; ++i) start[i + 1] = start[i] + int64_t(weight(i / plan.token_tiles)) * kblocks;
+    std::vector<int64_t> cut(plan.grid + 1, 0);  // positions in blocks: item * kblocks + kb
+    cut[plan.grid] = int64_t(items) * kblocks;
+    int item = 0;
+    for (int c = 1; c < plan.grid; ++c) {
+      const int64_t v = total_cost * c / plan.grid;
+      while (item + 1 < items && start[item + 1] <= v) ++item;
+      const int w = weight(item / plan.token_tiles);
+      int kb = int((v - start[item] + w / 2) / w);
+      if (kb < kMinBlocks) kb = 0;
+      if (kblocks - kb < kMinBlocks) kb = kblocks;
+      cut[c] = std::max(cut[c - 1], int64_t(item) * kblocks + kb);
+    }
+    plan.units.clear();
+    plan.cta_begin.assign(1, 0);
+    std::vector<int> pieces(items, 0);
+    for (int c = 0; c < plan.grid; ++c) {
+      for (int64_t pos = cut[c]; pos < cut[c + 1];) {
+        const int i = int(pos / kblocks), kb = int(pos % kblocks);
+        const int end = int(std::min<int64_t>(kblocks, cut[c + 1] - int64_t(i) * kblocks));
+        plan.units.push_back(WorkUnit{i / plan.token_tiles, i % plan.token_tiles, kb, end, pieces[i]++, 1, 0, 0});
+        pos = int64_t(i) * kblocks + end;
+      }
+      plan.cta_begin.push_back(int(plan.units.size()));
+    }
+    int slots = 0, counters = 0;
+    std::vector<int> slot_of(items, 0), counter_of(items, 0);
+    for (int i = 0; i < items; ++i)
+      if (pieces[i] > 1) { slot_of[i] = slots; counter_of[i] = counters++; slots += pieces[i]; }
+    for (auto& unit : plan.units) {
+      const int i = unit.tile * plan.token_tiles + unit.token_tile;
+      unit.nsplit = pieces[i];
+      unit.ws_slot = slot_of[i];
+      unit.counter = counter_of[i];
+    }
+    plan.ws_slots = slots;
+    plan.counters = counters;
+  };
+
+  if (schedule == HG_SCHEDULE_AUTO) {
+    // Data-parallel when whole tiles already balance to within 10 % of the ideal
+    // share; otherwise stream-K, which balances by construction.
+    const int64_t worst = greedy(dp, dp_cost);
+    const double ideal = double(total_cost) / std::min<int64_t>(sms, std::max<int64_t>(1, total_cost));
+    schedule = (items >= sms && double(worst) <= 1.10 * ideal) ? HG_SCHEDULE_DATA_PARALLEL : HG_SCHEDULE_STREAM_K;
+  }
+  plan.ws_slots = 0;
+  plan.counters = 0;
+  if (schedule == HG_SCHEDULE_DATA_PARALLEL) {
+    greedy(dp, dp_cost);
+  } else if (schedule == HG_SCHEDULE_SPLIT_K) {
+    const int splits = std::max<int>(1, std::min<int64_t>(kblocks, (2 * int64_t(sms) * kblocks + total_cost - 1) / std::max<int64_t>(1, total_cost)));
+    split_k(splits);
+  } else if (schedule == HG_SCHEDULE_STREAM_K) {
+    stream_k();
+  } else {
+    throw std::runtime_error("Unknown tile schedule id");
+  }
+  plan.schedule = schedule;
+  return plan;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side: tensor maps, handle, launch
+// ---------------------------------------------------------------------------------------------
+
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiled encode_tiled() {
+  static EncodeTiled fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiled>(ptr);
+  });
+  if (!fn) throw std::runtime_error("cuTensorMapEncodeTiled is not available from this driver");
+  return fn;
+}
+
+// 2-D K-major tensor map: dim0 = K elements, dim1 = rows; box = 128 x box_rows, 128B swizzle.
+static CUtensorMap make_map(const void* ptr, bool fp4, int rows, int k, int box_rows) {
+  CUtensorMap map;
+  std::memset(&map, 0, sizeof(map));
+  const cuuint64_t dims[2] = {cuuint64_t(k), cuuint64_t(rows)};
+  const cuuint64_t strides[1] = {cuuint64_t(fp4 ? k / 2 : k)};
+  const cuuint32_t box[2] = {128u, cuuint32_t(box_rows)};
+  const cuuint32_t elem[2] = {1u, 1u};
+  const CUresult r = encode_tiled()(&map, fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                                    const_cast<void*>(ptr), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string(int(r)));
+  return map;
+}
+
+struct TcGemm {
+  Plan plan;
+  int rows[2] = {0, 0}, tokens = 0, k = 0, outputs = 0, dtype = HG_DTYPE_BF16;
+  WorkUnit* d_units = nullptr;
+  int* d_cta_begin = nullptr;
+  float* d_workspace = nullptr;
+  int* d_counters = nullptr;
+  int* d_status = nullptr;
+};
+
+static void validate(const hg_problem& l, const hg_problem& h) {
+  const hg_problem& any = l.rows ? l : h;
+  if (l.rows < 0 || h.rows < 0 || l.rows + h.rows == 0) throw std::runtime_error("Hybrid GEMM needs at least one weight row");
+  if (any.tokens <= 0 || any.k <= 0 || any.k % 128 || any.outputs <= 0) throw std::runtime_error("Invalid hybrid GEMM shape");
+  if (l.rows && h.rows &&
+      (l.tokens != h.tokens || l.k != h.k || l.outputs != h.outputs || l.activation != h.activation ||
+       l.activation_scales != h.activation_scales || l.output != h.output))
+    throw std::runtime_error("Low and high partitions must share activation, scales and output");
+  auto misaligned = [](const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) != 0; };
+  for (const hg_problem* q : {&l, &h}) {
+    if (!q->rows) continue;
+    if (!q->weight || !q->activation || !q->weight_scales || !q->activation_scales || !q->ids || !q->output)
+      throw std::runtime_error("Null pointer in hybrid GEMM problem");
+    if (misaligned(q->weight, 32) || misaligned(q->activation, 16) || misaligned(q->weight_scales, 16) ||
+        misaligned(q->activation_scales, 16) || misaligned(q->ids, 4) || misaligned(q->output, 2))
+      throw std::runtime_error("Hybrid GEMM operands must be aligned (weights 32 B, codes and scales 16 B)");
+  }
+}
+
+template <typename T>
+static void configure_kernel(int smem_bytes) {
+  check(cudaFuncSetAttribute(hybrid_gemm_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes),
+        "cudaFuncSetAttribute");
+}
+
+TcGemm* tc_create(const hg_problem& l, const hg_problem& h, int schedule, int dtype, cudaStream_t stream) {
+  validate(l, h);
+  if (dtype != HG_DTYPE_F16 && dtype != HG_DTYPE_BF16) throw std::runtime_error("Unknown output dtype");
+  const hg_problem& any = l.rows ? l : h;
+  int device = 0, sms = 0;
+  check(cudaGetDevice(&device), "cudaGetDevice");
+  check(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device), "SM count");
+  auto g = std::make_unique<TcGemm>();
+  g->rows[0] = l.rows; g->rows[1] = h.rows;
+  g->tokens = any.tokens; g->k = any.k; g->outputs = any.outputs; g->dtype = dtype;
+  g->plan = make_plan(l.rows, h.rows, any.tokens, any.k, sms, schedule);
+  const Plan& plan = g->plan;
+  check(cudaMalloc(&g->d_units, sizeof(WorkUnit) * std::max<size_t>(1, plan.units.size())), "cudaMalloc units");
+  check(cudaMalloc(&g->d_cta_begin, sizeof(int) * plan.cta_begin.size()), "cudaMalloc schedule");
+  check(cudaMalloc(&g->d_workspace, sizeof(float) * std::max<int64_t>(1, int64_t(plan.ws_slots) * plan.n_tile * kTileRows)), "cudaMalloc workspace");
+  check(cudaMalloc(&g->d_counters, sizeof(int) * std::max(1, plan.counters)), "cudaMalloc counters");
+  check(cudaMalloc(&g->d_status, sizeof(int) * 4), "cudaMalloc status");
+  check(cudaMemcpyAsync(g->d_units, plan.units.data(), sizeof(WorkUnit) * plan.units.size(), cudaMemcpyHostToDevice, stream), "upload units");
+  check(cudaMemcpyAsync(g->d_cta_begin, plan.cta_begin.data(), sizeof(int) * plan.cta_begin.size(), cudaMemcpyHostToDevice, stream), "upload schedule");
+  check(cudaMemsetAsync(g->d_counters, 0, sizeof(int) * std::max(1, plan.counters), stream), "clear counters");
+  check(cudaMemsetAsync(g->d_status, 0, sizeof(int) * 4, stream), "clear status");
+  check(cudaStreamSynchronize(stream), "schedule upload");  // host vectors are pageable
+  if (dtype == HG_DTYPE_BF16) configure_kernel<__nv_bfloat16>(plan.smem_bytes);
+  else configure_kernel<__half>(plan.smem_bytes);
+  return g.release();
+}
+
+void tc_run(TcGemm* g, const hg_problem& l, const hg_problem& h, cudaStream_t stream) {
+  validate(l, h);
+  const hg_problem& any = l.rows ? l : h;
+  if (l.rows != g->rows[0] || h.rows != g->rows[1] || any.tokens != g->tokens || any.k != g->k || any.outputs != g->outputs)
+    throw std::runtime_error("Hybrid GEMM handle was created for a different shape");
+  const Plan& plan = g->plan;
+  TcParams p{};
+  p.rows[0] = l.rows; p.rows[1] = h.rows;
+  p.tiles[0] = (l.rows + kTileRows - 1) / kTileRows; p.tiles[1] = (h.rows + kTileRows - 1) / kTileRows;
+  p.sfa[0] = static_cast<const uint8_t*>(l.weight_scales); p.sfa[1] = static_cast<const uint8_t*>(h.weight_scales);
+  p.ids[0] = static_cast<const int32_t*>(l.ids); p.ids[1] = static_cast<const int32_t*>(h.ids);
+  p.sfb = static_cast<const uint8_t*>(any.activation_scales);
+  p.out = static_cast<uint16_t*>(any.output);
+  p.outputs = any.outputs; p.tokens = any.tokens; p.k = any.k; p.kblocks = any.k / kTileK;
+  p.n_tile = plan.n_tile; p.stages = plan.stages; p.dtype = g->dtype; p.tmem_cols = uint32_t(plan.tmem_cols);
+  p.units = g->d_units; p.cta_begin = g->d_cta_begin;
+  p.workspace = g->d_workspace; p.counters = g->d_counters; p.status = g->d_status;
+  // An absent partition still needs a valid descriptor; it is never dereferenced.
+  const CUtensorMap map_act = make_map(any.activation, false, any.tokens, any.k, plan.n_tile);
+  const CUtensorMap map_low = l.rows ? make_map(l.weight, true, l.rows, l.k, kTileRows) : map_act;
+  const CUtensorMap map_high = h.rows ? make_map(h.weight, false, h.rows, h.k, kTileRows) : map_act;
+  if (g->dtype == HG_DTYPE_BF16)
+    hybrid_gemm_tc_kernel<__nv_bfloat16><<<plan.grid, kTcThreads, plan.smem_bytes, stream>>>(p, map_low, map_high, map_act);
+  else
+    hybrid_gemm_tc_kernel<__half><<<plan.grid, kTcThreads, plan.smem_bytes, stream>>>(p, map_low, map_high, map_act);
+  check(cudaGetLastError(), "hybrid GEMM launch");
+}
+
+void tc_destroy(TcGemm* g) {
+  if (!g) return;
+  cudaFree(g->d_units); cudaFree(g->d_cta_begin); cudaFree(g->d_workspace); cudaFree(g->d_counters); cudaFree(g->d_status);
+  delete g;
+}
+
+const Plan& tc_plan(const TcGemm* g) { return g->plan; }
+
+void tc_kernel_attributes(int* registers, int* local_bytes) {
+  cudaFuncAttributes attr{};
+  check(cudaFuncGetAttributes(&attr, hybrid_gemm_tc_kernel<__nv_bfloat16>), "cudaFuncGetAttributes");
+  *registers = attr.numRegs;
+  *local_bytes = int(attr.localSizeBytes);
+}
+
+void tc_status(TcGemm* g, cudaStream_t stream, int out[3]) {
+  int host[4] = {0, 0, 0, 0};
+  check(cudaMemcpyAsync(host, g->d_status, sizeof(host), cudaMemcpyDeviceToHost, stream), "status read");
+  check(cudaMemsetAsync(g->d_status, 0, sizeof(host), stream), "status clear");
+  check(cudaStreamSynchronize(stream), "status sync");
+  out[0] = host[0]; out[1] = host[1]; out[2] = host[2];
+}
+
+}  // namespace hg

@@ -1,0 +1,55 @@
+// Host-side interface of the tcgen05 hybrid GEMM (see hg_gemm_tc.cu).
+#pragma once
+#include <vector>
+
+#include "hg_common.cuh"
+
+namespace hg {
+
+constexpr int kTileRows = 128;  // weight rows per output tile (MMA M)
+constexpr int kTileK = 128;     // K elements per pipeline stage
+constexpr int kMaxStages = 12;
+constexpr int kTcThreads = 192; // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
+
+// One contiguous run of K128 blocks of one (row tile, token tile).
+struct WorkUnit {
+  int tile;        // virtual row tile: [0,tiles_low) low partition, then the high partition
+  int token_tile;  // index of the token tile (n_tile tokens each)
+  int kb_begin, kb_end;
+  int split;       // position of this unit among the tile's units, in K order
+  int nsplit;      // units the tile is cut into (1 = direct scatter, no workspace)
+  int ws_slot;     // first workspace slot of the tile (valid when nsplit > 1)
+  int counter;     // arrival counter of the tile (valid when nsplit > 1)
+};
+
+struct Plan {
+  int n_tile = 0;          // tokens per tile = MMA N
+  int token_tiles = 0;
+  int stages = 0;
+  int grid = 0;
+  int schedule = 0;        // HG_SCHEDULE_* actually used
+  int smem_bytes = 0;
+  int tmem_cols = 0;
+  int ws_slots = 0;        // fp32 [n_tile][128] slots
+  int counters = 0;
+  std::vector<WorkUnit> units;
+  std::vector<int> cta_begin;  // grid + 1 offsets into units
+};
+
+// Builds the tile schedule for one shape.  `sms` is the SM count of the device,
+// `schedule` one of HG_SCHEDULE_{AUTO,DATA_PARALLEL,SPLIT_K,STREAM_K}.
+Plan make_plan(int rows_low, int rows_high, int tokens, int k, int sms, int schedule);
+
+struct TcGemm;  // opaque device-side state (plan buffers, workspace, counters, status)
+TcGemm* tc_create(const hg_problem& l, const hg_problem& h, int schedule, int dtype, cudaStream_t stream);
+void tc_run(TcGemm*, const hg_problem& l, const hg_problem& h, cudaStream_t stream);
+void tc_destroy(TcGemm*);
+const Plan& tc_plan(const TcGemm*);
+void tc_kernel_attributes(int* registers, int* local_bytes);
+// Reads (and clears) the device status words: [0] error code of a bounded wait
+// that gave up, [1] K128 blocks issued to the tensor core, [2] work units stored.
+void tc_status(TcGemm*, cudaStream_t stream, int out[3]);
+
+void run_simt_pair(const hg_problem& l, const hg_problem& h, cudaStream_t stream, int tokens_per_pass, int dtype);
+
+}  // namespace hg

@@ -1,0 +1,131 @@
+/*
+ * C ABI of the B200 (sm_100a) hybrid MXFP4/MXFP8 output-channel linear layer.
+ *
+ * Every symbol the reference's Python binds through ctypes is exported with
+ * the same name, argument order and error convention, so the reference's
+ * `hygemm_vllm/native.py`, `producer.py` and `fused.py` can load this library
+ * unchanged (HYGEMM_LIBRARY / HYGEMM_PRODUCER_LIBRARY / HYGEMM_FUSED_LIBRARY
+ * may all point at the one shared object).  The reference's entry points keep
+ * their IEEE-half meaning; `_bf16` / `_dtype` twins add bfloat16, the primary
+ * type of this build.
+ *
+ * Ownership: the caller owns every tensor; the library borrows pointers for
+ * the duration of the enqueued work and owns only a handle's workspace.
+ * Errors: `int` status, 0 = ok, -1 = failure with a thread-local message in
+ * hg_last_error() (hg_silu_pack returns a cudaError_t value instead, as the
+ * reference does).  No C++ exception crosses the boundary.  All pointers are
+ * device pointers unless stated; `stream` is a cudaStream_t.
+ *
+ * Citations name the reference interface each declaration replaces
+ * (paths relative to the reference project root).
+ */
+#ifndef HYGEMM_B200_H_
+#define HYGEMM_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* One precision partition of a hybrid linear.
+ * Replaces hygemm::oc::DeviceProblem (src/kernel/output_channel_gemm.h:14-22)
+ * == ctypes `Problem` (integrations/vllm/hygemm_vllm/native.py:7-9).
+ * output[token * outputs + ids[row]] = dot(W[row], X[token]). */
+typedef struct hg_problem {
+  int rows;                      /* weight rows in this partition (0 = partition absent) */
+  int tokens;                    /* M */
+  int k;                         /* input channels, multiple of 128 */
+  int outputs;                   /* N of the full layer (row stride of output) */
+  const void* weight;            /* packed E2M1 [rows,k/2] (low) or E4M3 [rows,k] (high) */
+  const void* activation;        /* E4M3 [tokens,k], shared by both partitions */
+  const void* weight_scales;     /* E8M0, 512-byte atoms of 128 rows x 4 K32 groups */
+  const void* activation_scales; /* E8M0, same layout, hg_scale_size(tokens,k) bytes */
+  const void* ids;               /* int32 [rows] output channel of each row */
+  void* output;                  /* 16-bit float [tokens,outputs] */
+} hg_problem;
+
+enum { HG_DTYPE_F16 = 0, HG_DTYPE_BF16 = 1 };
+
+/* Launch policies accepted by hg_run (integrations/vllm/hygemm_vllm/native.py:14-15).
+ * 0..3 (serial, concurrent, high_first, high_main) all map to the single
+ * tcgen05 launch that covers both partitions; 4..6 select the SIMT pair kernel. */
+enum { HG_POLICY_SERIAL = 0, HG_POLICY_CONCURRENT = 1, HG_POLICY_HIGH_FIRST = 2, HG_POLICY_HIGH_MAIN = 3,
+       HG_POLICY_GEMV_PAIR1 = 4, HG_POLICY_GEMV_PAIR2 = 5, HG_POLICY_GEMV_PAIR4 = 6 };
+
+/* Schedule ids accepted as low_id/high_id by hg_create (the reference's
+ * variant ids, src/kernel/output_channel_gemm.h:41, select CUTLASS tile
+ * shapes; here they select the tile schedule of the one tcgen05 kernel). */
+enum { HG_SCHEDULE_AUTO = 0,        /* chosen from the shape and the SM count */
+       HG_SCHEDULE_DATA_PARALLEL = 1, /* one work unit per output tile */
+       HG_SCHEDULE_SPLIT_K = 2,     /* fixed split of K, deterministic fix-up */
+       HG_SCHEDULE_STREAM_K = 3,    /* equal k-block share per CTA */
+       HG_SCHEDULE_SIMT = 28 };     /* SIMT kernel (reference ids 28-34, output_channel_gemv.cu) */
+
+/* integrations/vllm/native/runtime.cu:116 */
+const char* hg_last_error(void);
+
+/* integrations/vllm/native/runtime.cu:117-119 — bytes of the padded scale buffer. */
+int64_t hg_scale_size(int rows, int k);
+
+/* integrations/vllm/native/runtime.cu:120-134 — quantise IEEE-half [rows,k] to
+ * E4M3 (fp4=0) or packed E2M1 (fp4=1) codes plus E8M0 scales; all padding bytes 0x7f. */
+int hg_pack(const void* in, void* out, void* sf, int rows, int k, int fp4, void* stream);
+/* integrations/vllm/native/runtime.cu:135-145 — mode only picks a kernel; bytes are identical. */
+int hg_pack_mode(const void* in, void* out, void* sf, int rows, int k, int fp4, void* stream, int mode);
+/* bfloat16 twins of the two above. */
+int hg_pack_bf16(const void* in, void* out, void* sf, int rows, int k, int fp4, void* stream);
+int hg_pack_mode_bf16(const void* in, void* out, void* sf, int rows, int k, int fp4, void* stream, int mode);
+
+/* integrations/vllm/native/producer.cu:46-54 — SwiGLU + MXFP8 quantisation of
+ * [rows,2k] gate||up; debug (optional) receives the 16-bit product.  Returns a
+ * cudaError_t value (0 = ok). */
+int hg_silu_pack(const void* in, void* q, void* sf, void* debug, int rows, int k, void* stream, int math);
+int hg_silu_pack_bf16(const void* in, void* q, void* sf, void* debug, int rows, int k, void* stream, int math);
+
+/* integrations/vllm/native/runtime.cu:146-147 — build the schedule and workspace
+ * for this exact shape (IEEE-half output).  A partition with rows==0 is skipped. */
+int hg_create(int low_id, int high_id, const hg_problem* low, const hg_problem* high, void* stream, void** handle);
+/* Same with an explicit output type (HG_DTYPE_*). */
+int hg_create_dtype(int low_id, int high_id, const hg_problem* low, const hg_problem* high, void* stream,
+                    int dtype, void** handle);
+/* integrations/vllm/native/runtime.cu:148-149 — rebind pointers (same shape) and
+ * enqueue on `stream`; allocates nothing; may be captured in a CUDA graph. */
+int hg_run(void* handle, const hg_problem* low, const hg_problem* high, void* stream, int policy);
+/* integrations/vllm/native/runtime.cu:151-161 — 10 ints per partition: id, tile_m,
+ * tile_n, tile_k, stages, registers, shared bytes, local bytes, fp8, pingpong (-1 if absent). */
+int hg_info(void* handle, int* out20);
+/* integrations/vllm/native/runtime.cu:162 */
+void hg_destroy(void* handle);
+/* Device-side status of the last launches of this handle: 0 = ok, otherwise the
+ * code a bounded in-kernel wait recorded before giving up.  status[3] = {error,
+ * K128 blocks issued, work units stored} since the last call; clears them and
+ * synchronises `stream`.
+ * (The reference has no counterpart; its kernels cannot report a stuck wait.) */
+int hg_status(void* handle, void* stream, int* status);
+/* Host-only view of the tile schedule hg_create would build for a shape on a
+ * device with `sms` SMs (no GPU needed; no counterpart in the reference, whose
+ * schedules live inside CUTLASS).  header[10] = schedule, grid, n_tile,
+ * token_tiles, stages, shared bytes, TMEM columns, workspace slots, counters,
+ * units; units (optional) receives 9 ints per unit: cta, tile, token_tile,
+ * kb_begin, kb_end, split, nsplit, ws_slot, counter. */
+int hg_plan(int rows_low, int rows_high, int tokens, int k, int sms, int schedule, int* header, int* units,
+            int max_units);
+
+/* Single-kernel path kept for binding compatibility
+ * (integrations/vllm/native/fused_probe.cu:7-28).  The tcgen05 kernel already
+ * covers both partitions in one launch, so these wrap the same implementation
+ * with operands fixed at creation. */
+const char* hg_fused_error(void);
+int hg_fused_create(int id, const hg_problem* low, const hg_problem* high, void* stream, void** handle);
+int hg_fused_create_dtype(int id, const hg_problem* low, const hg_problem* high, void* stream, int dtype,
+                          void** handle);
+int hg_fused_update(void* handle, const hg_problem* low, const hg_problem* high);
+int hg_fused_run(void* handle, void* stream);
+int hg_fused_info(void* handle, int* out11);
+void hg_fused_destroy(void* handle);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HYGEMM_B200_H_ */
