@@ -1,0 +1,469 @@
+"""Benchmark of the hybrid MXFP4/MXFP8 linear hot path on B200.
+
+Workload (`config.workload`): the Qwen2.5-7B layer-shape sweep — qkv 3584->4608,
+o_proj 3584->3584, gate_up 3584->37888, down 18944->3584 (10 % MXFP8 channels
+rounded to a multiple of 128), M in {1,2,4,8,16,32,64,128}.  One STEP is one
+pass of that sweep: for every M, one layer's worth of the hot path —
+quantise(x) -> qkv GEMM, quantise -> o_proj GEMM, quantise -> gate_up GEMM,
+SwiGLU+quantise -> down GEMM (8 kernels per M, 64 per step).  Two distinct
+weight sets (272 MB) alternate between consecutive M so every GEMM streams its
+weights from HBM, not from L2.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+* `value`: whole-job TFLOP/s (2*M*N*K over all GEMMs of the timed steps) with
+  inputs resident in HBM, the step replayed as one CUDA graph.
+* `e2e`: the same metric through the plugin-facing Python API
+  (`DualLinear.__call__`, `linear_silu` path) with HOST buffers: pinned-host ->
+  device copies of the step's activations and device -> host reads of its
+  outputs inside the timed region.
+* `roofline`: the tcgen05 GEMM kernel; algorithmic bytes per launch
+  (L*K/2 + H*K + N*K/32 + 4N + M*K + M*K/32 + 2*M*N) over the CUDA-event
+  duration of each launch in the same weight-cycling sequence.
+* `cpu_baseline`: the PyTorch port of the reference's dequantise-and-matmul path
+  on the host cores, on a bounded sample of the workload.
+* N > 1: the layer is sharded by tensor parallelism (column-parallel qkv /
+  gate_up on N, row-parallel o_proj / down on K with an NCCL all-reduce);
+  total work is fixed, so `scaling` is "strong".
+* `--impl reference`: the CPU port alone, same metric and unit (rank 0 only).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for p in (ROOT, ROOT / "comp2029-hybridgemm_b200"):
+    if str(p) not in sys.path:
+        sys.path.insert(0, str(p))
+
+import torch  # noqa: E402
+
+SEED = 20261024
+HIDDEN, INTER = 3584, 18944
+M_SWEEP = [1, 2, 4, 8, 16, 32, 64, 128]
+# name: (K, {projection: width}) of the unsharded layer
+SHAPES = {"qkv": (HIDDEN, {"q": 3584, "k": 512, "v": 512}), "o_proj": (HIDDEN, {"o": HIDDEN}),
+          "gate_up": (HIDDEN, {"gate": INTER, "up": INTER}), "down": (INTER, {"down": HIDDEN})}
+ROW_PARALLEL = {"o_proj", "down"}
+METRIC = "hybrid_gemm_tflops_qwen2.5-7b_layer_sweep_M1-128"
+
+
+def high_quota(n: int) -> int:
+    return 128 * round(0.1 * n / 128)
+
+
+def gemm_bytes(m, k, n, h):
+    """Algorithmic HBM bytes of one hybrid GEMM call."""
+    low = n - h
+    return low * k // 2 + h * k + n * k // 32 + 4 * n + m * k + m * k // 32 + 2 * m * n
+
+
+def k_block_shard(k: int, rank: int, world: int) -> tuple[int, int]:
+    """Row-parallel K range of `rank`, in whole K128 blocks (uneven when blocks % world != 0)."""
+    blocks = k // 128
+    base, rem = divmod(blocks, world)
+    begin = rank * base + min(rank, rem)
+    return begin * 128, (begin + base + (1 if rank < rem else 0)) * 128
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------------
+
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.samples, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self, begin: float, end: float) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        rows = [r for t, r in self.samples if begin - 0.05 <= t <= end + 0.15 and len(r) >= 7] or \
+               [r for _, r in self.samples if len(r) >= 7]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in rows)]
+
+        def num(s):
+            try:
+                return float(s)
+            except ValueError:
+                return None
+        sm = [num(r[0]) for r in rows if num(r[0]) is not None]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": num(rows[0][1]),
+                "power_w_max": max((num(r[2]) or 0) for r in rows), "samples": len(rows), "reasons": reasons}
+
+
+# ------------------------------------------------------------------------------------------------
+# workload
+# ------------------------------------------------------------------------------------------------
+
+def build_layer(device, layer_seed: int, rank: int, world: int):
+    """One transformer layer's four hybrid linears (this rank's tensor-parallel shard)."""
+    from hygemm_vllm import native
+    g = torch.Generator().manual_seed(layer_seed)
+    layer = {}
+    for name, (k, parts) in SHAPES.items():
+        n = sum(parts.values())
+        w = (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16)
+        high = torch.sort(torch.randperm(n, generator=g)[: high_quota(n)]).values
+        if world > 1:
+            if name in ROW_PARALLEL:
+                begin, end = k_block_shard(k, rank, world)
+                w = w[:, begin:end].contiguous()
+            else:
+                keep, offset = [], 0
+                for width in parts.values():
+                    step = width // world
+                    keep.append(torch.arange(offset + rank * step, offset + (rank + 1) * step))
+                    offset += width
+                keep = torch.cat(keep)
+                mask = torch.zeros(n, dtype=torch.bool)
+                mask[high] = True
+                w = w[keep].contiguous()
+                high = torch.where(mask[keep])[0]
+        layer[name] = native.DualLinear(w.to(device), high.to(device))
+    return layer
+
+
+def shard_stats(layer):
+    """(K, N, H) of each GEMM as this rank runs it."""
+    return {name: (rt.k, rt.outputs, int(rt.hi.numel())) for name, rt in layer.items()}
+
+
+class Sweep:
+    """Device buffers and the launch sequence of one step."""
+
+    def __init__(self, device, layers, world, group):
+        from hygemm_vllm import native, producer
+        self.native, self.producer = native, producer
+        self.layers, self.world, self.group, self.device = layers, world, group, device
+        g = torch.Generator().manual_seed(SEED + 1)
+        self.host, self.dev = {}, {}
+        k_o = layers[0]["o_proj"].k
+        for m in M_SWEEP:
+            x = torch.randn(3, m, HIDDEN, generator=g)
+            cols = torch.randperm(HIDDEN, generator=g)[: -(-HIDDEN // 100)]
+            x[:, :, cols] *= 20
+            x = x.to(torch.bfloat16)
+            self.host[m] = {"x_qkv": x[0].contiguous().pin_memory(), "x_gate": x[2].contiguous().pin_memory(),
+                            "x_o": x[1][:, :k_o].contiguous().pin_memory()}
+            self.dev[m] = {n: t.to(device) for n, t in self.host[m].items()}
+        self.launches_per_step = 8 * len(M_SWEEP)
+
+    def layer_for(self, i):
+        return self.layers[i % len(self.layers)]
+
+    def run_m(self, i, m, x, events=None):
+        """One layer's hot path at M tokens.  `events` (optional) collects (name, m, start, end) around GEMMs."""
+        layer = self.layer_for(i)
+        native, producer = self.native, self.producer
+        out = {}
+
+        def gemm(name, q, sf):
+            if events is None:
+                return layer[name].run_packed(q, sf)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            y = layer[name].run_packed(q, sf)
+            b.record()
+            events.append((name, m, a, b))
+            return y
+
+        out["qkv"] = gemm("qkv", *native.pack(x["x_qkv"]))
+        y_o = gemm("o_proj", *native.pack(x["x_o"]))
+        gate_up = gemm("gate_up", *native.pack(x["x_gate"]))
+        y_d = gemm("down", *producer.silu_pack(gate_up, 0))
+        if self.world > 1:
+            torch.distributed.all_reduce(y_o, group=self.group)
+            torch.distributed.all_reduce(y_d, group=self.group)
+        out["o_proj"], out["down"] = y_o, y_d
+        return out
+
+    def step_resident(self, events=None):
+        outs = None
+        for i, m in enumerate(M_SWEEP):
+            outs = self.run_m(i, m, self.dev[m], events)
+        return outs
+
+    def step_e2e(self, host_out):
+        """Host buffers in, host buffers out: the call a user of the plugin-facing API makes."""
+        h2d = d2h = 0
+        for i, m in enumerate(M_SWEEP):
+            x = {n: t.to(self.device, non_blocking=True) for n, t in self.host[m].items()}
+            h2d += sum(t.numel() * t.element_size() for t in self.host[m].values())
+            out = self.run_m(i, m, x)
+            for name in ("qkv", "o_proj", "down"):
+                host_out[m][name].copy_(out[name], non_blocking=True)
+                d2h += out[name].numel() * out[name].element_size()
+        return h2d, d2h
+
+
+def total_flops(stats):
+    return sum(2 * m * n * k for m in M_SWEEP for (k, n, h) in stats.values())
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU baseline (the oracle port; the only place the benchmark executes oracle code)
+# ------------------------------------------------------------------------------------------------
+
+_CPU_CASES = None
+
+
+def _cpu_cases():
+    """Quantised qkv and o_proj operands of the CPU sample (prepared once, outside any timed region)."""
+    global _CPU_CASES
+    if _CPU_CASES is None:
+        import oracle
+        g = torch.Generator().manual_seed(SEED)
+        cases = []
+        for name in ("qkv", "o_proj"):
+            k, parts = SHAPES[name]
+            n = sum(parts.values())
+            w = (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16)
+            high = torch.sort(torch.randperm(n, generator=g)[: high_quota(n)]).values.numpy()
+            lo, hi = oracle.partition(n, high)
+            w4, sf4 = oracle.pack(w[torch.from_numpy(lo).long()], fp4=True)
+            w8, sf8 = oracle.pack(w[torch.from_numpy(hi).long()], fp4=False)
+            xs = {m: torch.randn(m, k, generator=g).to(torch.bfloat16) for m in (1, 16, 128)}
+            cases.append((k, n, lo, hi, w4, sf4, w8, sf8, xs))
+        _CPU_CASES = cases
+    return _CPU_CASES
+
+
+def cpu_reference_sample(min_seconds: float = 0.0, passes: int = 1):
+    """Bounded sample of the workload on the host cores: qkv and o_proj shapes at M in {1,16,128} through the
+    PyTorch port of the reference's `reference()` (activations quantised, weights re-dequantised per call,
+    fp32 matmul — what the reference literally does).  Runs `passes` passes, then more until `min_seconds`."""
+    from oracle import torch_path
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    cases = _cpu_cases()
+    flops, done, begin = 0, 0, time.perf_counter()
+    while done < passes or time.perf_counter() - begin < min_seconds:
+        for k, n, lo, hi, w4, sf4, w8, sf8, xs in cases:
+            for m, x in xs.items():
+                torch_path.reference_linear(x, w4, sf4, lo, w8, sf8, hi, n, redequantise=True)
+                flops += 2 * m * n * k
+        done += 1
+    seconds = time.perf_counter() - begin
+    return {"value": flops / seconds / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+            "sample": f"qkv+o_proj shapes x M in (1,16,128), {done} pass(es), weights re-dequantised per call "
+                      f"as reference() does; {seconds:.1f} s of CPU work"}, seconds
+
+
+def run_reference_arm(args, rank):
+    if rank != 0:
+        return
+    for _ in range(args.warmup):                              # page-in, thread pool
+        cpu_reference_sample()
+    base, seconds = cpu_reference_sample(passes=args.steps)   # one step = one pass over the sample
+    value = base["value"]
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * seconds / max(1, args.steps),
+            "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None,
+            "dtype": "mxfp4/mxfp8 x mxfp8 -> fp32 accumulate -> bf16", "data": "synthetic",
+            "config": {"workload": "Qwen2.5-7B layer-shape GEMM sweep (bounded CPU sample: qkv + o_proj, M in 1/16/128)"},
+            "cpu_baseline": base,
+            "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------------
+# main
+# ------------------------------------------------------------------------------------------------
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(3, args.warmup)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} needs WORLD_SIZE={args.gpus} (launch with torch.distributed.run); got {world}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    import torch.distributed as dist
+    group = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+        group = dist.group.WORLD
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    layers = [build_layer(device, SEED + 100 * i, rank, world) for i in range(2)]
+    stats = shard_stats(layers[0])
+    sweep = Sweep(device, layers, world, group)
+    flops_step_rank = total_flops(stats)
+    flops_step = flops_step_rank
+    if world > 1:
+        t = torch.tensor([float(flops_step_rank)], device=device, dtype=torch.float64)
+        dist.all_reduce(t)
+        flops_step = t.item()
+
+    # ---- warm every shape (handles are created outside capture), then capture the step as a graph
+    for _ in range(2):
+        sweep.step_resident()
+    barrier()
+    graph = None
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            sweep.step_resident()
+    except Exception as exc:                                   # e.g. a collective that cannot be captured
+        graph = None
+        torch.cuda.synchronize()
+        note = f"step not graph-captured ({type(exc).__name__}); eager launches timed"
+    else:
+        note = "step replayed as one CUDA graph"
+
+    def one_step():
+        if graph is not None:
+            graph.replay()
+        else:
+            sweep.step_resident()
+
+    for _ in range(args.warmup):
+        one_step()
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    begin_wall = time.time()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        one_step()
+    stop.record()
+    barrier()
+    end_wall = time.time()
+    ms = start.elapsed_time(stop)
+    clocks = sampler.stop(begin_wall, end_wall) if sampler else None
+    if world > 1:
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+    value = flops_step * args.steps / (ms * 1e-3) / 1e12
+
+    # ---- end to end through the plugin-facing API with host buffers
+    host_out = {m: {"qkv": torch.empty(m, layers[0]["qkv"].outputs, dtype=torch.bfloat16).pin_memory(),
+                    "o_proj": torch.empty(m, HIDDEN, dtype=torch.bfloat16).pin_memory(),
+                    "down": torch.empty(m, HIDDEN, dtype=torch.bfloat16).pin_memory()} for m in M_SWEEP}
+    for _ in range(args.warmup):
+        sweep.step_e2e(host_out)
+    barrier()
+    e2e_steps = max(3, min(args.steps, 20))
+    start.record()
+    for _ in range(e2e_steps):
+        h2d, d2h = sweep.step_e2e(host_out)
+    stop.record()
+    barrier()
+    e2e_ms = start.elapsed_time(stop)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = t.item()
+    e2e_value = flops_step * e2e_steps / (e2e_ms * 1e-3) / 1e12
+
+    # ---- per-launch GEMM durations in the same weight-cycling sequence (CUDA events on the launch stream)
+    events = []
+    for _ in range(5):
+        sweep.step_resident(events)
+    torch.cuda.synchronize()
+    per = {}
+    for name, m, a, b in events:
+        per.setdefault((name, m), []).append(a.elapsed_time(b) * 1e-3)
+    status = [rt.status() for layer in layers for rt in layer.values()]
+    if any(s[0] for s in status):
+        raise SystemExit(f"device reported a stuck wait: {status}")
+
+    if rank == 0:
+        peaks = {}
+        peaks_file = ROOT / "MEASURED_PEAKS.json"
+        if peaks_file.exists():
+            peaks = json.loads(peaks_file.read_text())
+        hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+        sweep_rows, bytes_sum, time_sum = [], 0, 0.0
+        for (name, m), durations in sorted(per.items(), key=lambda kv: (list(SHAPES).index(kv[0][0]), kv[0][1])):
+            k, n, h = stats[name]
+            seconds = statistics.median(durations)
+            nbytes = gemm_bytes(m, k, n, h)
+            bytes_sum += nbytes
+            time_sum += seconds
+            sweep_rows.append({"gemm": name, "M": m, "K": k, "N": n, "H": h, "us": round(seconds * 1e6, 2),
+                               "GBps": round(nbytes / seconds / 1e9, 1), "TFLOPs": round(2 * m * n * k / seconds / 1e12, 2),
+                               "hbm_frac": round(nbytes / seconds / 1e9 / hbm_peak, 3)})
+        achieved = bytes_sum / time_sum / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+            "dtype": "mxfp4/mxfp8 x mxfp8 -> fp32 accumulate -> bf16", "data": "synthetic",
+            "config": {"workload": "Qwen2.5-7B layer-shape hybrid GEMM sweep: qkv 3584->4608, o_proj 3584->3584, "
+                                   "gate_up 3584->37888, down 18944->3584; M in 1,2,4,8,16,32,64,128; 10% MXFP8 channels",
+                       "step": "per M: quantise+qkv, quantise+o_proj, quantise+gate_up, SwiGLU-quantise+down",
+                       "parallelism": f"tp{world}" if world > 1 else "single GPU",
+                       "l2": "inputs larger than L2: two weight sets (272 MB) alternate between consecutive M",
+                       "launch": note, "seed": SEED},
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps,
+                    "api": "hygemm_vllm.native.DualLinear.__call__ / producer.silu_pack + run_packed, eager"},
+            "gpu_launches": sweep.launches_per_step * args.steps,
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                         "frac": achieved / hbm_peak, "traffic": None,
+                         "kernel": "hybrid_gemm_tc_kernel", "peak_source": "of measured" if peaks else "of fallback",
+                         "how": "sum of algorithmic bytes of the 32 GEMM launches of a step / sum of their median "
+                                "CUDA-event durations (5 instrumented steps, same weight cycling)"},
+            "sweep": sweep_rows,
+        }
+        if not args.no_cpu_baseline and world == 1:
+            cpu_reference_sample()
+            line["cpu_baseline"], _ = cpu_reference_sample(min_seconds=10.0)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -417,6 +417,7 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
 // ---------------------------------------------------------------------------------------------
 
 static int round_up(int v, int m) { return (v + m - 1) / m * m; }
+constexpr int kMaxDynamicSmem = 232448;  // 227 KiB, the per-CTA limit of sm_100
 
 Plan make_plan(int rows_low, int rows_high, int tokens, int k, int sms, int schedule) {
   Plan plan;
@@ -425,7 +426,7 @@ Plan make_plan(int rows_low, int rows_high, int tokens, int k, int sms, int sche
   plan.n_tile = tokens >= 128 ? 128 : std::max(16, round_up(tokens, 16));
   plan.token_tiles = (tokens + plan.n_tile - 1) / plan.n_tile;
   const int stage_bytes = 16384 + plan.n_tile * 128 + 1024;
-  plan.stages = std::min(kMaxStages, (232448 - 1024 - kBarrierBytes) / stage_bytes);
+  plan.stages = std::min(kMaxStages, (kMaxDynamicSmem - 1024 - kBarrierBytes) / stage_bytes);
   plan.smem_bytes = 1024 + plan.stages * stage_bytes + kBarrierBytes;
   int cols = 2 * round_up(plan.n_tile, 32) + 16, pow2 = 32;
   while (pow2 < cols) pow2 *= 2;
@@ -628,9 +629,11 @@ static void validate(const hg_problem& l, const hg_problem& h) {
   }
 }
 
+// The limit is a property of the function, not of a handle: always raise it to the device maximum so
+// handles with different stage counts can coexist.
 template <typename T>
-static void configure_kernel(int smem_bytes) {
-  check(cudaFuncSetAttribute(hybrid_gemm_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes),
+static void configure_kernel() {
+  check(cudaFuncSetAttribute(hybrid_gemm_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem),
         "cudaFuncSetAttribute");
 }
 
@@ -656,8 +659,8 @@ TcGemm* tc_create(const hg_problem& l, const hg_problem& h, int schedule, int dt
   check(cudaMemsetAsync(g->d_counters, 0, sizeof(int) * std::max(1, plan.counters), stream), "clear counters");
   check(cudaMemsetAsync(g->d_status, 0, sizeof(int) * 4, stream), "clear status");
   check(cudaStreamSynchronize(stream), "schedule upload");  // host vectors are pageable
-  if (dtype == HG_DTYPE_BF16) configure_kernel<__nv_bfloat16>(plan.smem_bytes);
-  else configure_kernel<__half>(plan.smem_bytes);
+  if (dtype == HG_DTYPE_BF16) configure_kernel<__nv_bfloat16>();
+  else configure_kernel<__half>();
   return g.release();
 }
 
