@@ -297,6 +297,79 @@ def run_reference_arm(args, rank):
 
 
 # ------------------------------------------------------------------------------------------------
+# single-GEMM mode (small, self-ending case for ncu captures)
+# ------------------------------------------------------------------------------------------------
+
+def run_single_gemm(args, device):
+    """`--gemm NAME:M[:SCHEDULE]`: one shape, `steps` launches alternating between enough weight copies to
+    exceed L2, each bracketed by CUDA events; prints one JSON line with the median duration."""
+    from hygemm_vllm import native
+    fields = args.gemm.split(":")
+    name, m = fields[0], int(fields[1])
+    schedule = int(fields[2]) if len(fields) > 2 else 0
+    k, parts = SHAPES[name]
+    n = sum(parts.values())
+    h = high_quota(n) if len(fields) < 4 else int(round(float(fields[3]) * n))
+    weight_bytes = (n - h) * k // 2 + h * k
+    copies = max(2, -(-300_000_000 // weight_bytes))            # > 2x the 126 MB L2 between reuses
+    g = torch.Generator().manual_seed(SEED)
+    w = (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16).to(device)
+    high = torch.sort(torch.randperm(n, generator=g)[:h]).values.to(device)
+    layers = []
+    for c in range(copies):
+        layers.append(native.DualLinear(torch.roll(w, c, 0) if c else w, high, schedule, schedule))
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(device)
+    q, sf = native.pack(x)
+    for layer in layers[:2]:
+        layer.run_packed(q, sf)
+    torch.cuda.synchronize()
+    import ctypes as C
+    stream = torch.cuda.current_stream().cuda_stream
+    for layer in layers:
+        if not layer.handles:
+            layer.run_packed(q, sf)
+    y = torch.empty((m, n), dtype=torch.bfloat16, device=device)
+    calls = []
+    for layer in layers:
+        low, hi = layer.problems(q, sf, y)
+        calls.append((layer.handles[next(iter(layer.handles))], low, hi))
+    lib = native.library()
+
+    def enqueue(count):
+        stream = torch.cuda.current_stream().cuda_stream      # the capture stream while a graph is recorded
+        for i in range(count):
+            handle, low, hi = calls[i % copies]
+            native.check(lib.hg_run(handle, C.byref(low), C.byref(hi), stream, 0))
+
+    # `count` launches back to back (weight copies cycled) as one CUDA graph, so the host launch rate
+    # does not bound what is measured; one event pair around each replay.
+    count = max(args.steps, copies)
+    enqueue(copies)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        enqueue(count)
+    stream = torch.cuda.current_stream().cuda_stream
+    times = []
+    for _ in range(6):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b) * 1e-3 / count)
+    times = times[1:]
+    seconds = statistics.median(times)
+    nbytes = gemm_bytes(m, k, n, h)
+    info = layers[0].info(m)
+    print(json.dumps({"gemm": name, "M": m, "K": k, "N": n, "H": h, "schedule": info[0], "n_tile": info[2],
+                      "stages": info[4], "copies": copies, "us_median": seconds * 1e6, "us_min": min(times) * 1e6,
+                      "GBps": nbytes / seconds / 1e9, "algorithmic_bytes": nbytes,
+                      "status": [layer.status() for layer in layers][:2]}))
+
+
+# ------------------------------------------------------------------------------------------------
 # main
 # ------------------------------------------------------------------------------------------------
 
@@ -307,6 +380,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gemm", default=None, metavar="NAME:M[:SCHEDULE[:HIGH_FRACTION]]",
+                    help="profiling aid: run only this GEMM (e.g. gate_up:16) a few times on cold weights and exit")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     rank = int(os.environ.get("RANK", "0"))
@@ -321,6 +396,9 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    if args.gemm:
+        run_single_gemm(args, device)
+        return
     import torch.distributed as dist
     group = None
     if world > 1:

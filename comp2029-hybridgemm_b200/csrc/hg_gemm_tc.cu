@@ -31,6 +31,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <mutex>
@@ -52,6 +53,8 @@ struct TcParams {
   uint16_t* out;
   int outputs, tokens, k, kblocks;
   int n_tile, stages, dtype;
+  int issuers;    // MMA-issuing threads = independent accumulators per unit (1, 2 or 4)
+  const uint8_t* weight_low;
   uint32_t tmem_cols;
   const WorkUnit* units;
   const int* cta_begin;
@@ -60,8 +63,8 @@ struct TcParams {
   int* status;
 };
 
-enum : int { kErrProducer = 1, kErrMmaFull = 2, kErrMmaAcc = 3, kErrEpilogue = 4, kErrDrain = 5 };
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait
+enum : int { kErrProducer = 1, kErrMmaFull = 2, kErrMmaAcc = 3, kErrEpilogue = 4, kErrDrain = 5, kErrLoader = 6 };
+constexpr long long kWaitLimitCycles = 4000000000ll;  // about 2 s at the boost clock, per wait
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
 
@@ -95,15 +98,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 
 // Bounded wait.  Returns false when the limit expired or another role of this
-// CTA already gave up (abort flag in shared memory).
+// CTA already gave up (abort flag in shared memory).  The clock is only read on
+// the slow path, every 256 failed polls (each poll itself blocks in hardware for
+// a short, implementation-defined time).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long start = global_timer();
+#pragma unroll 1
+  for (int burst = 0; burst < 256; ++burst)
+    if (mbar_try_wait(bar, parity)) return true;
+  const long long start = clock64();
+#pragma unroll 1
   for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((spin & 63u) == 0) {
+    if ((spin & 255u) == 0) {
       if (*abort_flag) return false;
-      if (global_timer() - start > kWaitLimitNs) return false;
+      if (clock64() - start > kWaitLimitCycles) return false;
     }
   }
 }
@@ -184,26 +192,41 @@ __device__ __forceinline__ void scatter_store(uint16_t* out, int64_t index, floa
   out[index] = from_float<T>(v);
 }
 
+// Shared-memory plan.  One pipeline stage covers up to two K128 blocks (K256):
+//   A   2 x 16 KiB  weight tiles, 128 rows x 128 B each, 128B-swizzled, K-major
+//   B   2 x n_tile x 128 B activation tiles, same layout
+//   SFA 2 x 512 B, SFB 2 x 512 B scale atoms
 struct SmemLayout {
   uint32_t a, b, sfa, sfb, bars;  // byte offsets from the 1024-aligned base
-  uint32_t b_stage;
+  uint32_t b_tile;                // bytes of one K128 activation tile
 };
 __host__ __device__ inline SmemLayout smem_layout(int stages, int n_tile) {
   SmemLayout s;
-  s.b_stage = uint32_t(n_tile) * 128u;
+  s.b_tile = uint32_t(n_tile) * 128u;
   s.a = 0;
-  s.b = s.a + uint32_t(stages) * 16384u;
-  s.sfa = s.b + uint32_t(stages) * s.b_stage;
-  s.sfb = s.sfa + uint32_t(stages) * 512u;
-  s.bars = s.sfb + uint32_t(stages) * 512u;
+  s.b = s.a + uint32_t(stages) * 32768u;
+  s.sfa = s.b + uint32_t(stages) * 2u * s.b_tile;
+  s.sfb = s.sfa + uint32_t(stages) * 1024u;
+  s.bars = s.sfb + uint32_t(stages) * 1024u;
   return s;
 }
+constexpr int kScaleSets = 2;  // TMEM scale-factor buffers, alternated per K128 block
 constexpr int kBarrierBytes = (2 * kMaxStages + 5) * 8 + 32;
+constexpr int kLoaderThreads = 128;  // warps 6..9
+
+// 8-byte asynchronous copy global -> shared; src_bytes = 0 writes zeros instead.
+__device__ __forceinline__ void cp_async_8(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+// One arrival on `bar` once every cp.async this thread issued so far has landed.
+__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
 
 template <typename T>
 __global__ void __launch_bounds__(kTcThreads, 1)
-hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant__ CUtensorMap map_low,
-                      const __grid_constant__ CUtensorMap map_high, const __grid_constant__ CUtensorMap map_act) {
+hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant__ CUtensorMap map_high,
+                      const __grid_constant__ CUtensorMap map_act) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -224,15 +247,17 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_high)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_act)) : "memory");
     for (int s = 0; s < p.stages; ++s) {
-      mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), 1);
+      mbar_init(full_bar(s), 1 + kLoaderThreads);  // TMA thread (with the byte count) + every loader thread
+      mbar_init(empty_bar(s), 1);                  // released by the MMA thread's commit
     }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(acc_full_bar(s), 1);
+      mbar_init(acc_full_bar(s), uint32_t(p.issuers));
       mbar_init(acc_empty_bar(s), 4);
     }
-    mbar_init(drain_bar, 1);
+    mbar_init(drain_bar, uint32_t(p.issuers));
     *abort_flag = 0;
     *ticket_slot = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -249,8 +274,10 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = uint32_t(*tmem_slot);
 
-  // TMEM columns: two accumulators, then two sets of (SFA, SFB), 4 columns each.
-  const uint32_t acc_stride = uint32_t((p.n_tile + 31) & ~31);
+  // TMEM columns: two accumulator slots of issuers x acc_cols columns, then per issuer kScaleSets sets
+  // of (SFA, SFB), 4 columns each.
+  const uint32_t acc_cols = uint32_t((p.n_tile + 31) & ~31);
+  const uint32_t acc_stride = acc_cols * uint32_t(p.issuers);
   const uint32_t sf_cols = tmem_base + 2 * acc_stride;
 
   const int unit_begin = p.cta_begin[blockIdx.x], unit_end = p.cta_begin[blockIdx.x + 1];
@@ -258,70 +285,140 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
+    // Activations, both scale streams and MXFP8 weight tiles (128-byte rows).  MXFP4 weight
+    // tiles are brought in by the loader warps below.
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      const uint32_t tx_common = lay.b_stage + 1024u;
       for (int u = unit_begin; u < unit_end && !error; ++u) {
         const WorkUnit wu = p.units[u];
         const int part = wu.tile >= p.tiles[0];
         const int tile = part ? wu.tile - p.tiles[0] : wu.tile;
-        const CUtensorMap* map_w = part ? &map_high : &map_low;
-        const uint32_t tx = tx_common + (part ? 16384u : 8192u);
         const int token0 = wu.token_tile * p.n_tile;
         const uint8_t* sfa_src = p.sfa[part] + (int64_t(tile) * p.kblocks) * 512;
         const uint8_t* sfb_src = p.sfb + (int64_t(token0 / 128) * p.kblocks) * 512;
-        for (int kb = wu.kb_begin; kb < wu.kb_end; ++kb) {
+        for (int kb = wu.kb_begin; kb < wu.kb_end; kb += 2) {
+          const int nkb = min(2, wu.kb_end - kb);
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { error = kErrProducer; break; }
           const uint32_t bar = full_bar(stage);
-          mbar_expect_tx(bar, tx);
-          tma_load_2d(base + lay.a + uint32_t(stage) * 16384u, map_w, bar, kb * kTileK, tile * kTileRows);
-          tma_load_2d(base + lay.b + uint32_t(stage) * lay.b_stage, &map_act, bar, kb * kTileK, token0);
-          bulk_load(base + lay.sfa + uint32_t(stage) * 512u, sfa_src + int64_t(kb) * 512, 512u, bar);
-          bulk_load(base + lay.sfb + uint32_t(stage) * 512u, sfb_src + int64_t(kb) * 512, 512u, bar);
+          mbar_expect_tx(bar, uint32_t(nkb) * ((part ? 16384u : 0u) + lay.b_tile + 1024u));
+          for (int i = 0; i < nkb; ++i) {
+            if (part)
+              tma_load_2d(base + lay.a + uint32_t(stage) * 32768u + uint32_t(i) * 16384u, &map_high, bar,
+                          (kb + i) * kTileK, tile * kTileRows);
+            tma_load_2d(base + lay.b + (uint32_t(stage) * 2u + uint32_t(i)) * lay.b_tile, &map_act, bar,
+                        (kb + i) * kTileK, token0);
+          }
+          bulk_load(base + lay.sfa + uint32_t(stage) * 1024u, sfa_src + int64_t(kb) * 512, uint32_t(nkb) * 512u, bar);
+          bulk_load(base + lay.sfb + uint32_t(stage) * 1024u, sfb_src + int64_t(kb) * 512, uint32_t(nkb) * 512u, bar);
           if (++stage == p.stages) { stage = 0; phase ^= 1u; }
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0, kiter = 0, issued = 0;
+  } else if (warp >= 6 && warp < 10) {
+    // ------------------------------------------------------------------ MXFP4 weight loaders (warps 6..9)
+    // The f8f6f4 MMA kinds read 4-bit operands from an 8-bit container: every 16-byte chunk of a
+    // shared-memory row holds 16 codes in its first 8 bytes and 8 bytes of padding.  Each thread copies
+    // 8-byte granules of the packed rows (16 codes) straight to the first half of their swizzled chunk
+    // with cp.async, so HBM carries 0.5 B/element, requests are full 128-byte lines (sixteen
+    // consecutive lanes cover one row's K256 slice) and no register or staging buffer is involved.
+    // Thread t owns granule m = t % 16 of rows t / 16 + 8 i; row % 8 is constant per thread, so the
+    // swizzle term is too.
+    const int t = threadIdx.x - 192;
+    const int m = t & 15, rsub = t >> 4;
+    const int blk = m >> 3, j = m & 7;
+    const uint32_t dst_off = uint32_t(blk) * 16384u + uint32_t(rsub) * 128u + (uint32_t(j ^ rsub) << 4);
+    const int64_t pitch = p.k >> 1;  // bytes per packed row
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int u = unit_begin; u < unit_end && !error; ++u) {
+      const WorkUnit wu = p.units[u];
+      const int part = wu.tile >= p.tiles[0];
+      const int row0 = wu.tile * kTileRows + rsub;  // first row of this thread (low partition only)
+      const uint8_t* src0 = p.weight_low + int64_t(row0) * pitch + m * 8;
+      for (int kb = wu.kb_begin; kb < wu.kb_end; kb += 2) {
+        const int nkb = min(2, wu.kb_end - kb);
+        bool ok = true;
+        if (lane == 0) ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag);
+        ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;
+        if (!ok) { error = kErrLoader; break; }
+        if (!part && blk < nkb) {
+          const uint32_t dst = base + lay.a + uint32_t(stage) * 32768u + dst_off;
+          const uint8_t* src = src0 + int64_t(kb) * 64;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const bool valid = row0 + 8 * i < p.rows[0];
+            cp_async_8(dst + uint32_t(i) * 1024u, valid ? src + int64_t(8 * i) * pitch : p.weight_low, valid ? 8u : 0u);
+          }
+        }
+        cp_async_arrive(full_bar(stage));
+        if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+      }
+    }
+    // Copies still in flight must land before shared memory is released.
+    asm volatile("cp.async.wait_all;" ::: "memory");
+  } else if (warp == 1 || warp >= 10) {
+    // ------------------------------------------------------------------ MMA issuers (warps 1, 10, 11, 12)
+    // A tcgen05 instruction costs its issuing thread on the order of a hundred cycles (descriptor set-up
+    // through the uniform datapath) whatever its shape, far more than a 128 x n_tile x 32 MMA occupies the
+    // tensor core.  So up to four threads in four warps issue independent streams: issuer q takes pipeline
+    // every I-th pipeline stage and accumulates into its own TMEM accumulator; the epilogue adds the
+    // accumulators in a fixed order, which keeps the result deterministic.
+    const int q = warp == 1 ? 0 : warp - 9;
+    if (lane == 0 && q < p.issuers) {
+      uint32_t issued = 0;
       int acc_it = 0;
-      // SFB of token tile t0 sits in column (t0 % 128) / 32 of its 128-token atom.
+      uint32_t ring = 0;                                   // pipeline stages consumed by earlier units
+      const uint32_t sf_base = sf_cols + uint32_t(q) * (8u * kScaleSets);
+      uint32_t sf_flip = 0;
       for (int u = unit_begin; u < unit_end && !error; ++u, ++acc_it) {
         const WorkUnit wu = p.units[u];
         const int part = wu.tile >= p.tiles[0];
         const int slot = acc_it & 1;
+        const uint32_t unit_stages = uint32_t(wu.kb_end - wu.kb_begin + 1) >> 1;
         if (!mbar_wait(acc_empty_bar(slot), (uint32_t(acc_it >> 1) & 1u) ^ 1u, abort_flag)) { error = kErrMmaAcc; break; }
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + uint32_t(slot) * acc_stride;
+        const uint32_t tmem_d = tmem_base + uint32_t(slot) * acc_stride + uint32_t(q) * acc_cols;
         const uint32_t idesc = instr_desc(part == 0, p.n_tile);
+        // SFB of token tile t0 sits in column (t0 % 128) / 32 of its 128-token atom.
         const uint32_t sfb_col = uint32_t((wu.token_tile * p.n_tile) % 128) / 32u;
-        for (int kb = wu.kb_begin; kb < wu.kb_end; ++kb, ++kiter) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag)) { error = kErrMmaFull; break; }
+        // Ownership follows the GLOBAL stage number g (g % issuers == q).  The ring depth is a multiple of
+        // the issuer count, so each ring slot, and with it each full/empty barrier, has exactly one
+        // consumer that sees every round in turn; parity waits stay unambiguous however short units are.
+        const uint32_t first = (uint32_t(q) + uint32_t(p.issuers) - ring % uint32_t(p.issuers)) % uint32_t(p.issuers);
+        for (uint32_t l = first; l < unit_stages && !error; l += uint32_t(p.issuers)) {
+          const int kb = wu.kb_begin + 2 * int(l);
+          const int nkb = min(2, wu.kb_end - kb);
+          const uint32_t g = ring + l;
+          const int stage = int(g % uint32_t(p.stages));
+          if (!mbar_wait(full_bar(stage), (g / uint32_t(p.stages)) & 1u, abort_flag)) { error = kErrMmaFull; break; }
+          // The MXFP4 rows were written through the generic proxy (cp.async); the tensor core reads
+          // shared memory through the async proxy.
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           tc_fence_after();
-          const uint32_t sf_set = sf_cols + (kiter & 1u) * 8u;
-          tc_cp_scales(sf_set, smem_desc(base + lay.sfa + uint32_t(stage) * 512u, 0, 128, kSwizzleNone));
-          tc_cp_scales(sf_set + 4, smem_desc(base + lay.sfb + uint32_t(stage) * 512u, 0, 128, kSwizzleNone));
-          const uint64_t desc_a = smem_desc(base + lay.a + uint32_t(stage) * 16384u, 0, 1024, kSwizzle128B);
-          const uint64_t desc_b = smem_desc(base + lay.b + uint32_t(stage) * lay.b_stage, 0, 1024, kSwizzle128B);
+          for (int i = 0; i < nkb; ++i) {
+            const uint32_t sf_set = sf_base + (sf_flip ^= 1u) * 8u;
+            tc_cp_scales(sf_set, smem_desc(base + lay.sfa + uint32_t(stage) * 1024u + uint32_t(i) * 512u, 0, 128, kSwizzleNone));
+            tc_cp_scales(sf_set + 4, smem_desc(base + lay.sfb + uint32_t(stage) * 1024u + uint32_t(i) * 512u, 0, 128, kSwizzleNone));
+            const uint64_t desc_a = smem_desc(base + lay.a + uint32_t(stage) * 32768u + uint32_t(i) * 16384u, 0, 1024, kSwizzle128B);
+            const uint64_t desc_b = smem_desc(base + lay.b + (uint32_t(stage) * 2u + uint32_t(i)) * lay.b_tile, 0, 1024, kSwizzle128B);
 #pragma unroll
-          for (uint32_t j = 0; j < 4; ++j) {
-            // 32 K-elements = 32 bytes further along the swizzled row: start address field += 2.
-            tc_mma(tmem_d, desc_a + 2 * j, desc_b + 2 * j, idesc | (j << 29) | (j << 4),
-                   (kb > wu.kb_begin || j > 0) ? 1u : 0u, sf_set, sf_set + 4 + sfb_col);
+            for (uint32_t j = 0; j < 4; ++j) {
+              // 32 K-elements = 32 bytes further along the swizzled row: start address field += 2.
+              tc_mma(tmem_d, desc_a + 2 * j, desc_b + 2 * j, idesc | (j << 29) | (j << 4),
+                     (l > first || i > 0 || j > 0) ? 1u : 0u, sf_set, sf_set + 4 + sfb_col);
+            }
+            ++issued;
           }
           tc_commit(empty_bar(stage));
-          ++issued;
-          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
         }
+        ring += unit_stages;
+        // Every issuer reports, also one that had no stage in this unit (its accumulator is then skipped).
         if (!error) tc_commit(acc_full_bar(slot));
       }
       // Let every MMA issued by this thread retire before TMEM is released.
       tc_commit(drain_bar);
-      if (!mbar_wait(drain_bar, 0, abort_flag) && !error) error = kErrDrain;
+      if (q == 0 && !mbar_wait(drain_bar, 0, abort_flag) && !error) error = kErrDrain;
       if (issued) atomicAdd(p.status + 1, int(issued));
     }
   } else {
@@ -330,34 +427,49 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
     const int row_in_tile = quarter * 32 + lane;
     const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
     int acc_it = 0, stored = 0;
+    uint32_t ring = 0;
     for (int u = unit_begin; u < unit_end; ++u, ++acc_it) {
       const WorkUnit wu = p.units[u];
       const int part = wu.tile >= p.tiles[0];
       const int tile = part ? wu.tile - p.tiles[0] : wu.tile;
       const int slot = acc_it & 1;
+      const int row = tile * kTileRows + row_in_tile;
+      const bool row_ok = row < p.rows[part];
+      const int channel = row_ok ? p.ids[part][row] : 0;   // fetched while the main loop runs
       const bool ok = mbar_wait(acc_full_bar(slot), uint32_t(acc_it >> 1) & 1u, abort_flag);
       if (!epilogue_all(ok)) { error = kErrEpilogue; break; }
       tc_fence_after();
-      const int row = tile * kTileRows + row_in_tile;
-      const bool row_ok = row < p.rows[part];
-      const int channel = row_ok ? p.ids[part][row] : 0;
       const int token0 = wu.token_tile * p.n_tile;
+      // Issuers that owned a stage of this unit: global stages ring .. ring + unit_stages - 1, modulo issuers.
+      const uint32_t unit_stages = uint32_t(wu.kb_end - wu.kb_begin + 1) >> 1;
+      uint32_t owners = 0;
+      for (uint32_t l = 0; l < unit_stages && l < uint32_t(p.issuers); ++l) owners |= 1u << ((ring + l) % uint32_t(p.issuers));
+      ring += unit_stages;
       const uint32_t taddr = tmem_base + lane_addr + uint32_t(slot) * acc_stride;
       float* ws = wu.nsplit > 1
                       ? p.workspace + (int64_t(wu.ws_slot) + wu.split) * (int64_t(p.n_tile) * kTileRows) + row_in_tile
                       : nullptr;
-      for (int c0 = 0; c0 < p.n_tile; c0 += 8) {
-        uint32_t r[8];
-        tc_load8(taddr + uint32_t(c0), r);
-        tc_wait_ld();
+      for (int c0 = 0; c0 < p.n_tile; c0 += 16) {
+        float r[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) r[i] = 0.f;
+        for (int a = 0; a < p.issuers; ++a) {   // add the issuers' accumulators in a fixed order
+          if (!((owners >> a) & 1u)) continue;
+          uint32_t e[16];
+          tc_load8(taddr + uint32_t(a) * acc_cols + uint32_t(c0), *reinterpret_cast<uint32_t(*)[8]>(&e[0]));
+          tc_load8(taddr + uint32_t(a) * acc_cols + uint32_t(c0 + 8), *reinterpret_cast<uint32_t(*)[8]>(&e[8]));
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) r[i] += __uint_as_float(e[i]);
+        }
         if (ws) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) ws[int64_t(c0 + i) * kTileRows] = __uint_as_float(r[i]);
+          for (int i = 0; i < 16; ++i) ws[int64_t(c0 + i) * kTileRows] = r[i];
         } else if (row_ok) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
+          for (int i = 0; i < 16; ++i) {
             const int token = token0 + c0 + i;
-            if (token < p.tokens) scatter_store<T>(p.out, int64_t(token) * p.outputs + channel, __uint_as_float(r[i]));
+            if (token < p.tokens) scatter_store<T>(p.out, int64_t(token) * p.outputs + channel, r[i]);
           }
         }
       }
@@ -369,22 +481,27 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
       if (wu.nsplit > 1) {
         // Deterministic split-K fix-up: the last unit of the tile to arrive sums
         // all partials in K order.  No unit ever waits for another.
-        __threadfence();
         epilogue_sync();
-        if (threadIdx.x == 64) *ticket_slot = atomicAdd(p.counters + wu.counter, 1);
+        if (threadIdx.x == 64) {
+          __threadfence();   // cumulative: covers the partials of all epilogue threads ordered by the barrier
+          *ticket_slot = atomicAdd(p.counters + wu.counter, 1);
+        }
         epilogue_sync();
         const int ticket = *ticket_slot;
         if (ticket == wu.nsplit - 1) {
           __threadfence();
           const float* src = p.workspace + int64_t(wu.ws_slot) * (int64_t(p.n_tile) * kTileRows) + row_in_tile;
           if (row_ok) {
-            for (int c = 0; c < p.n_tile; ++c) {
-              const int token = token0 + c;
-              if (token >= p.tokens) break;
-              float sum = 0.f;
-              for (int s = 0; s < wu.nsplit; ++s)
-                sum += __ldcg(src + (int64_t(s) * p.n_tile + c) * kTileRows);
-              scatter_store<T>(p.out, int64_t(token) * p.outputs + channel, sum);
+            for (int c = 0; c < p.n_tile && token0 + c < p.tokens; c += 4) {
+              float sum[4] = {0.f, 0.f, 0.f, 0.f};
+              for (int s = 0; s < wu.nsplit; ++s) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) sum[i] += __ldcg(src + (int64_t(s) * p.n_tile + c + i) * kTileRows);
+              }
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                if (token0 + c + i < p.tokens)
+                  scatter_store<T>(p.out, int64_t(token0 + c + i) * p.outputs + channel, sum[i]);
             }
           }
           if (threadIdx.x == 64) p.counters[wu.counter] = 0;  // ready for the next launch
@@ -400,8 +517,8 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
     *abort_flag = 1;
     atomicCAS(p.status, 0, error * 1000000 + int(blockIdx.x));
     // Give copies and MMAs in flight time to land before shared memory and TMEM are released.
-    const unsigned long long start = global_timer();
-    while (global_timer() - start < 200000ull) __nanosleep(1000);
+    const long long start = clock64();
+    while (clock64() - start < 400000ll) __nanosleep(1000);
   }
   tc_fence_before();
   __syncthreads();
@@ -425,10 +542,20 @@ Plan make_plan(int rows_low, int rows_high, int tokens, int k, int sms, int sche
   const int tiles = tiles_low + tiles_high, kblocks = k / kTileK;
   plan.n_tile = tokens >= 128 ? 128 : std::max(16, round_up(tokens, 16));
   plan.token_tiles = (tokens + plan.n_tile - 1) / plan.n_tile;
-  const int stage_bytes = 16384 + plan.n_tile * 128 + 1024;
+  const int stage_bytes = 32768 + 2 * plan.n_tile * 128 + 2048;  // one K256 stage: weights, activations, scales
   plan.stages = std::min(kMaxStages, (kMaxDynamicSmem - 1024 - kBarrierBytes) / stage_bytes);
+  if (const char* cap = std::getenv("HYGEMM_TC_STAGES"))  // tuning aid: cap the pipeline depth
+    plan.stages = std::max(2, std::min(plan.stages, std::atoi(cap)));
   plan.smem_bytes = 1024 + plan.stages * stage_bytes + kBarrierBytes;
-  int cols = 2 * round_up(plan.n_tile, 32) + 16, pow2 = 32;
+  // MMA-issuing threads: two wherever TMEM holds two double-buffered accumulators per slot (512 columns
+  // in all); the pipeline depth is kept a multiple of the issuer count (see the kernel).
+  plan.issuers = plan.n_tile <= 64 ? 2 : 1;
+  if (const char* cap = std::getenv("HYGEMM_TC_ISSUERS"))  // tuning aid: 1, 2 or 4
+    plan.issuers = std::max(1, std::min(plan.n_tile <= 32 ? 4 : plan.issuers, std::atoi(cap)));
+  if (plan.issuers == 3) plan.issuers = 2;
+  plan.stages = std::max(plan.issuers, plan.stages / plan.issuers * plan.issuers);
+  plan.smem_bytes = 1024 + plan.stages * stage_bytes + kBarrierBytes;
+  int cols = plan.issuers * (2 * round_up(plan.n_tile, 32) + 8 * kScaleSets), pow2 = 32;
   while (pow2 < cols) pow2 *= 2;
   plan.tmem_cols = pow2;
 
@@ -540,11 +667,13 @@ Plan make_plan(int rows_low, int rows_high, int tokens, int k, int sms, int sche
   };
 
   if (schedule == HG_SCHEDULE_AUTO) {
-    // Data-parallel when whole tiles already balance to within 10 % of the ideal
-    // share; otherwise stream-K, which balances by construction.
-    const int64_t worst = greedy(dp, dp_cost);
-    const double ideal = double(total_cost) / std::min<int64_t>(sms, std::max<int64_t>(1, total_cost));
-    schedule = (items >= sms && double(worst) <= 1.10 * ideal) ? HG_SCHEDULE_DATA_PARALLEL : HG_SCHEDULE_STREAM_K;
+    // Measured on B200 (Qwen2.5-7B layer shapes, M = 1..128): whole tiles win once there are about
+    // 1.5 tiles per SM, and also for wide token tiles unless K is long, because the fix-up traffic of a
+    // cut tile grows with n_tile (n_tile x 128 fp32 partials written and read per piece); otherwise
+    // stream-K, which keeps every SM streaming.
+    const bool many_tiles = 2 * items >= 3 * sms;
+    const bool wide_short = plan.n_tile >= 64 && kblocks < 64;
+    schedule = (many_tiles || wide_short) ? HG_SCHEDULE_DATA_PARALLEL : HG_SCHEDULE_STREAM_K;
   }
   plan.ws_slots = 0;
   plan.counters = 0;
@@ -584,18 +713,17 @@ static EncodeTiled encode_tiled() {
   return fn;
 }
 
-// 2-D K-major tensor map: dim0 = K elements, dim1 = rows; box = 128 x box_rows, 128B swizzle.
-static CUtensorMap make_map(const void* ptr, bool fp4, int rows, int k, int box_rows) {
+// 2-D K-major tensor map over E4M3 bytes: dim0 = K, dim1 = rows; box = 128 x box_rows, 128B swizzle.
+static CUtensorMap make_map(const void* ptr, int rows, int k, int box_rows) {
   CUtensorMap map;
   std::memset(&map, 0, sizeof(map));
   const cuuint64_t dims[2] = {cuuint64_t(k), cuuint64_t(rows)};
-  const cuuint64_t strides[1] = {cuuint64_t(fp4 ? k / 2 : k)};
+  const cuuint64_t strides[1] = {cuuint64_t(k)};
   const cuuint32_t box[2] = {128u, cuuint32_t(box_rows)};
   const cuuint32_t elem[2] = {1u, 1u};
-  const CUresult r = encode_tiled()(&map, fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
-                                    const_cast<void*>(ptr), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const CUresult r = encode_tiled()(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box,
+                                    elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string(int(r)));
   return map;
 }
@@ -653,7 +781,7 @@ TcGemm* tc_create(const hg_problem& l, const hg_problem& h, int schedule, int dt
   check(cudaMalloc(&g->d_cta_begin, sizeof(int) * plan.cta_begin.size()), "cudaMalloc schedule");
   check(cudaMalloc(&g->d_workspace, sizeof(float) * std::max<int64_t>(1, int64_t(plan.ws_slots) * plan.n_tile * kTileRows)), "cudaMalloc workspace");
   check(cudaMalloc(&g->d_counters, sizeof(int) * std::max(1, plan.counters)), "cudaMalloc counters");
-  check(cudaMalloc(&g->d_status, sizeof(int) * 4), "cudaMalloc status");
+    check(cudaMalloc(&g->d_status, sizeof(int) * 4), "cudaMalloc status");
   check(cudaMemcpyAsync(g->d_units, plan.units.data(), sizeof(WorkUnit) * plan.units.size(), cudaMemcpyHostToDevice, stream), "upload units");
   check(cudaMemcpyAsync(g->d_cta_begin, plan.cta_begin.data(), sizeof(int) * plan.cta_begin.size(), cudaMemcpyHostToDevice, stream), "upload schedule");
   check(cudaMemsetAsync(g->d_counters, 0, sizeof(int) * std::max(1, plan.counters), stream), "clear counters");
@@ -679,16 +807,17 @@ void tc_run(TcGemm* g, const hg_problem& l, const hg_problem& h, cudaStream_t st
   p.out = static_cast<uint16_t*>(any.output);
   p.outputs = any.outputs; p.tokens = any.tokens; p.k = any.k; p.kblocks = any.k / kTileK;
   p.n_tile = plan.n_tile; p.stages = plan.stages; p.dtype = g->dtype; p.tmem_cols = uint32_t(plan.tmem_cols);
+  p.issuers = plan.issuers;
+  p.weight_low = static_cast<const uint8_t*>(l.weight);
   p.units = g->d_units; p.cta_begin = g->d_cta_begin;
   p.workspace = g->d_workspace; p.counters = g->d_counters; p.status = g->d_status;
-  // An absent partition still needs a valid descriptor; it is never dereferenced.
-  const CUtensorMap map_act = make_map(any.activation, false, any.tokens, any.k, plan.n_tile);
-  const CUtensorMap map_low = l.rows ? make_map(l.weight, true, l.rows, l.k, kTileRows) : map_act;
-  const CUtensorMap map_high = h.rows ? make_map(h.weight, false, h.rows, h.k, kTileRows) : map_act;
+  // An absent high partition still needs a valid descriptor; it is never dereferenced.
+  const CUtensorMap map_act = make_map(any.activation, any.tokens, any.k, plan.n_tile);
+  const CUtensorMap map_high = h.rows ? make_map(h.weight, h.rows, h.k, kTileRows) : map_act;
   if (g->dtype == HG_DTYPE_BF16)
-    hybrid_gemm_tc_kernel<__nv_bfloat16><<<plan.grid, kTcThreads, plan.smem_bytes, stream>>>(p, map_low, map_high, map_act);
+    hybrid_gemm_tc_kernel<__nv_bfloat16><<<plan.grid, kTcThreads, plan.smem_bytes, stream>>>(p, map_high, map_act);
   else
-    hybrid_gemm_tc_kernel<__half><<<plan.grid, kTcThreads, plan.smem_bytes, stream>>>(p, map_low, map_high, map_act);
+    hybrid_gemm_tc_kernel<__half><<<plan.grid, kTcThreads, plan.smem_bytes, stream>>>(p, map_high, map_act);
   check(cudaGetLastError(), "hybrid GEMM launch");
 }
 

@@ -9,7 +9,7 @@ namespace hg {
 constexpr int kTileRows = 128;  // weight rows per output tile (MMA M)
 constexpr int kTileK = 128;     // K elements per pipeline stage
 constexpr int kMaxStages = 12;
-constexpr int kTcThreads = 192; // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
+constexpr int kTcThreads = 416; // warp 0 TMA, 1 and 10-12 MMA issuers, 2-5 epilogue, 6-9 MXFP4 loaders
 
 // One contiguous run of K128 blocks of one (row tile, token tile).
 struct WorkUnit {
@@ -30,6 +30,7 @@ struct Plan {
   int schedule = 0;        // HG_SCHEDULE_* actually used
   int smem_bytes = 0;
   int tmem_cols = 0;
+  int issuers = 1;         // MMA-issuing threads, each with its own TMEM accumulator
   int ws_slots = 0;        // fp32 [n_tile][128] slots
   int counters = 0;
   std::vector<WorkUnit> units;

@@ -87,7 +87,7 @@ int hg_info(void* handle, int* out) {
   const hg::Plan& plan = hg::tc_plan(r->tc);
   for (int part = 0; part < 2; ++part) {
     if (!(part ? r->high.rows : r->low.rows)) continue;
-    const int values[10] = {plan.schedule, hg::kTileRows, plan.n_tile, hg::kTileK, plan.stages,
+    const int values[10] = {plan.schedule, hg::kTileRows, plan.n_tile, 2 * hg::kTileK, plan.stages,
                             regs, plan.smem_bytes, local, part, 0};
     std::copy(values, values + 10, out + part * 10);
   }
@@ -171,10 +171,11 @@ int hg_fused_info(void* handle, int* data) {
   int regs = 0, local = 0;
   hg::tc_kernel_attributes(&regs, &local);
   const hg::Plan& plan = hg::tc_plan(f->runner->tc);
-  const int common = plan.n_tile * 128 + 1024;
+  // Bytes per K256 stage: MXFP4 weights arrive by cp.async (16 KiB packed), MXFP8 by TMA (32 KiB).
+  const int common = 2 * (plan.n_tile * 128 + 1024);
   const int tiles = (f->low.rows + 127) / 128 + (f->high.rows + 127) / 128;
-  const int values[11] = {plan.schedule, hg::kTileRows, plan.n_tile, hg::kTileK, plan.stages, regs,
-                          plan.smem_bytes, local, 8192 + common, 16384 + common, tiles * 128};
+  const int values[11] = {plan.schedule, hg::kTileRows, plan.n_tile, 2 * hg::kTileK, plan.stages, regs,
+                          plan.smem_bytes, local, 16384 + common, 32768 + common, tiles * 128};
   std::copy(values, values + 11, data);
   HG_FUSED_CATCH
 }

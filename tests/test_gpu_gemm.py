@@ -137,7 +137,7 @@ def test_rebind_to_other_shape_is_rejected():
     assert b"shape" in lib.hg_last_error()
     info = (C.c_int * 20)()
     native.check(lib.hg_info(handle, info))
-    assert info[1] == 128 and info[3] == 128 and info[11] == 128 and info[8] == 0 and info[18] == 1
+    assert info[1] == 128 and info[3] == 256 and info[11] == 128 and info[8] == 0 and info[18] == 1
     lib.hg_destroy(handle)
     bad = native.Problem(0, 7, 256, 257, None, None, None, None, None, None)
     assert lib.hg_create_dtype(0, 0, C.byref(bad), C.byref(bad), None, 1, C.byref(handle)) == -1
