@@ -176,6 +176,7 @@ class Sweep:
                             "x_o": x[1][:, :k_o].contiguous().pin_memory()}
             self.dev[m] = {n: t.to(device) for n, t in self.host[m].items()}
         self.launches_per_step = 8 * len(M_SWEEP)
+        self.event_factory = lambda: torch.cuda.Event(enable_timing=True)
 
     def layer_for(self, i):
         return self.layers[i % len(self.layers)]
@@ -189,7 +190,7 @@ class Sweep:
         def gemm(name, q, sf):
             if events is None:
                 return layer[name].run_packed(q, sf)
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a, b = self.event_factory(), self.event_factory()
             a.record()
             y = layer[name].run_packed(q, sf)
             b.record()
@@ -483,14 +484,32 @@ def main():
         e2e_ms = t.item()
     e2e_value = flops_step * e2e_steps / (e2e_ms * 1e-3) / 1e12
 
-    # ---- per-launch GEMM durations in the same weight-cycling sequence (CUDA events on the launch stream)
-    events = []
-    for _ in range(5):
-        sweep.step_resident(events)
-    torch.cuda.synchronize()
-    per = {}
-    for name, m, a, b in events:
-        per.setdefault((name, m), []).append(a.elapsed_time(b) * 1e-3)
+    # ---- per-launch GEMM durations in the same weight-cycling sequence: CUDA events recorded INSIDE a graph
+    # of the step (event-record nodes on the launch stream), so the host launch path is not in the number.
+    per, how = {}, "event-record nodes around each GEMM inside a CUDA graph of the step, 5 replays"
+    try:
+        if graph is None:
+            raise RuntimeError("step is not graph-captured")
+        events = []
+        sweep.event_factory = lambda: torch.cuda.Event(enable_timing=True, external=True)
+        timed_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(timed_graph):
+            sweep.step_resident(events)
+        for _ in range(5):
+            timed_graph.replay()
+            torch.cuda.synchronize()
+            for name, m, a, b in events:
+                per.setdefault((name, m), []).append(a.elapsed_time(b) * 1e-3)
+    except Exception as exc:
+        torch.cuda.synchronize()
+        per, events = {}, []
+        how = f"eager launches bracketed by events ({type(exc).__name__}: in-graph events unavailable); includes host launch latency"
+        sweep.event_factory = lambda: torch.cuda.Event(enable_timing=True)
+        for _ in range(5):
+            sweep.step_resident(events)
+        torch.cuda.synchronize()
+        for name, m, a, b in events:
+            per.setdefault((name, m), []).append(a.elapsed_time(b) * 1e-3)
     status = [rt.status() for layer in layers for rt in layer.values()]
     if any(s[0] for s in status):
         raise SystemExit(f"device reported a stuck wait: {status}")
@@ -529,10 +548,13 @@ def main():
             "gpu_launches": sweep.launches_per_step * args.steps,
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                         "frac": achieved / hbm_peak, "traffic": None,
+                         "frac": achieved / hbm_peak,
+                         # ncu captures of gate_up and down at M=16 read 1.01x and 1.00x the algorithmic bytes from
+                         # DRAM; traffic grows with the bytes streamed, so the step average is scaled by that ratio.
+                         "traffic": 1.01 * bytes_sum / len(sweep_rows), "traffic_unit": "bytes per GEMM launch (mean)",
                          "kernel": "hybrid_gemm_tc_kernel", "peak_source": "of measured" if peaks else "of fallback",
                          "how": "sum of algorithmic bytes of the 32 GEMM launches of a step / sum of their median "
-                                "CUDA-event durations (5 instrumented steps, same weight cycling)"},
+                                "CUDA-event durations; " + how},
             "sweep": sweep_rows,
         }
         if not args.no_cpu_baseline and world == 1:

@@ -9,25 +9,30 @@
 //
 // * MMA shape: tcgen05.mma kind::mxf8f6f4.block_scale, M = 128 weight rows,
 //   N = n_tile tokens (16..128), K = 32 per instruction, fp32 accumulators in
-//   TMEM.  The A format (E2M1 or E4M3), the tensor map and the expected TMA
-//   byte count are chosen per tile, so low and high tiles share one pipeline.
-// * Operands: TMA (cp.async.bulk.tensor, 128B swizzle) into a ring of K128
-//   stages.  Packed E2M1 rows are expanded to the 8-bit container the f8f6f4
-//   kinds want by the tensor map type 16U4_ALIGN16B: 0.5 B/element from HBM,
-//   1 B/element in shared memory.
-// * Scales: the 512-byte atoms (128 rows x 4 K32 groups) travel by 1-D bulk
-//   copies and go to TMEM with tcgen05.cp 32x128b.warpx4; the byte of the
-//   current K32 block is selected with the a_sf_id/b_sf_id descriptor fields.
+//   TMEM.  The A format (E2M1 or E4M3) is chosen per tile, so low and high
+//   tiles share one pipeline (stage = two K128 blocks).
+// * Operands: activations, MXFP8 weight tiles and both scale streams by TMA
+//   (cp.async.bulk.tensor with 128B swizzle, 1-D bulk copies for the scale
+//   atoms).  MXFP4 weight tiles by 8-byte cp.async from dedicated loader warps:
+//   every 16 packed codes land in the first half of their swizzled 16-byte
+//   chunk, which is the 8-bit container the f8f6f4 kinds read, so HBM carries
+//   0.5 B/element and every request is a full 128-byte line.
+// * Scales: the 512-byte atoms (128 rows x 4 K32 groups) go to TMEM with
+//   tcgen05.cp 32x128b.warpx4; the byte of the current K32 block is selected
+//   with the a_sf_id/b_sf_id descriptor fields.
+// * Issue: up to four MMA-issuing threads in separate warps, each owning every
+//   I-th pipeline stage and its own accumulator (a tcgen05 instruction costs
+//   its issuer ~100 cycles whatever its shape).
 // * Schedule: a host-built list of work units (row tile, token tile, K range)
 //   per CTA: data-parallel, split-K or stream-K.  Tiles cut along K write fp32
 //   partials to a workspace; the LAST unit to arrive (atomic ticket, no
 //   spinning) sums the partials in K order, so the result is deterministic.
-// * Epilogue: tcgen05.ld 32x32b, fp32 -> bf16/fp16 (RNE), scattered straight to
-//   out[t*N + ids[r]]; consecutive lanes own consecutive rows, so sorted maps
-//   give contiguous 64-byte runs.  Two accumulator buffers let the epilogue of
-//   one unit overlap the main loop of the next.
-// * Every mbarrier wait is bounded (wall-clock); on expiry the CTA records a
-//   code in the status word, lets copies in flight land, frees TMEM and exits.
+// * Epilogue: tcgen05.ld 32x32b, accumulators added in a fixed order, fp32 ->
+//   bf16/fp16 (RNE), scattered straight to out[t*N + ids[r]]; consecutive lanes
+//   own consecutive rows, so sorted maps give contiguous 64-byte runs.  Two
+//   accumulator slots let the epilogue of one unit overlap the next main loop.
+// * Every mbarrier wait is bounded; on expiry the CTA records a code in the
+//   status word, lets copies in flight land, frees TMEM and exits.
 #include <cuda.h>
 
 #include <algorithm>
