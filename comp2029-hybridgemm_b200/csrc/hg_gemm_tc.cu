@@ -849,4 +849,124 @@ void tc_status(TcGemm* g, cudaStream_t stream, int out[3]) {
   out[0] = host[0]; out[1] = host[1]; out[2] = host[2];
 }
 
+// ---------------------------------------------------------------------------------------------
+// hg_run_static: the hybrid GEMM for callers that must not allocate device memory
+// ---------------------------------------------------------------------------------------------
+//
+// Some hosts of this library cannot call cudaMalloc on the path that runs a layer: a serving engine
+// that has handed all device memory to its own pool, a latency-critical loop where an allocation
+// (an implicit device-wide synchronisation) is not acceptable, or code that only ever sees shapes at
+// the moment it must run them and so cannot warm a handle first.  For them the scratch memory the
+// kernel needs — the tile schedule, the split-K partial sums, the arrival counters and the status
+// words — lives in one fixed array inside the library image instead of in a handle.
+//
+// * The array is HG_STATIC_SCRATCH_BYTES long on every GPU that loads the library, until exit.
+// * `g_static_scratch` is a device symbol.  Host code cannot use its name as a pointer; the device
+//   address is looked up once per device with cudaGetSymbolAddress, with that device current.  That
+//   look-up (and raising the kernel's shared-memory limit) happens in the first call on a device, so
+//   make that first call before any stream capture.
+// * All calls share the array: two calls that overlap on the GPU (different streams) race on it.
+//   Calls on one stream are ordered and safe.  Counters and status words are cleared at the start
+//   of every call, whatever an earlier call left behind.
+// * A shape whose schedule and partial sums do not fit is rejected with an error; nothing is launched.
+
+static __device__ __align__(256) unsigned char g_static_scratch[HG_STATIC_SCRATCH_BYTES];
+
+namespace {
+
+struct StaticState {
+  std::mutex mutex;
+  unsigned char* base[64] = {};   // device address of g_static_scratch, per device ordinal
+  int sms[64] = {};
+  bool have_plan = false;         // last schedule, reused while the shape repeats
+  int key[6] = {0, 0, 0, 0, 0, 0};
+  Plan plan;
+};
+
+StaticState& static_state() {
+  static StaticState state;
+  return state;
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+
+void tc_run_static(int schedule, const hg_problem& l, const hg_problem& h, int dtype, cudaStream_t stream) {
+  validate(l, h);
+  if (dtype != HG_DTYPE_F16 && dtype != HG_DTYPE_BF16) throw std::runtime_error("Unknown output dtype");
+  if (schedule < HG_SCHEDULE_AUTO || schedule > HG_SCHEDULE_STREAM_K) throw std::runtime_error("Unknown tile schedule id");
+  const hg_problem& any = l.rows ? l : h;
+  StaticState& st = static_state();
+  std::lock_guard<std::mutex> lock(st.mutex);
+  int device = 0;
+  check(cudaGetDevice(&device), "cudaGetDevice");
+  if (device < 0 || device >= 64) throw std::runtime_error("hg_run_static supports device ordinals 0..63");
+  if (!st.base[device]) {
+    // Once per device, with that device current: device address of the symbol, SM count, kernel limits.
+    void* address = nullptr;
+    check(cudaGetSymbolAddress(&address, g_static_scratch), "cudaGetSymbolAddress(static scratch)");
+    check(cudaDeviceGetAttribute(&st.sms[device], cudaDevAttrMultiProcessorCount, device), "SM count");
+    configure_kernel<__nv_bfloat16>();
+    configure_kernel<__half>();
+    st.base[device] = static_cast<unsigned char*>(address);
+  }
+  const int key[6] = {l.rows, h.rows, any.tokens, any.k, schedule, st.sms[device]};
+  if (!st.have_plan || std::memcmp(key, st.key, sizeof(key)) != 0) {
+    st.plan = make_plan(l.rows, h.rows, any.tokens, any.k, st.sms[device], schedule);
+    std::memcpy(st.key, key, sizeof(key));
+    st.have_plan = true;
+  }
+  const Plan& plan = st.plan;
+
+  // Carve the array: status | counters | cta_begin | units | workspace.
+  const size_t off_status = 0;
+  const size_t off_counters = 256;
+  const size_t off_cta = align_up(off_counters + sizeof(int) * size_t(std::max(1, plan.counters)), 256);
+  const size_t off_units = align_up(off_cta + sizeof(int) * plan.cta_begin.size(), 256);
+  const size_t off_work = align_up(off_units + sizeof(WorkUnit) * std::max<size_t>(1, plan.units.size()), 256);
+  const size_t total = off_work + sizeof(float) * size_t(plan.ws_slots) * size_t(plan.n_tile) * kTileRows;
+  if (total > size_t(HG_STATIC_SCRATCH_BYTES))
+    throw std::runtime_error("hg_run_static: this shape needs " + std::to_string(total) +
+                             " bytes of scratch (schedule and split-K partial sums) but the static buffer holds " +
+                             std::to_string(size_t(HG_STATIC_SCRATCH_BYTES)) + "; use hg_create/hg_run");
+  unsigned char* base = st.base[device];
+  check(cudaMemsetAsync(base, 0, off_cta, stream), "clear static status and counters");
+  check(cudaMemcpyAsync(base + off_cta, plan.cta_begin.data(), sizeof(int) * plan.cta_begin.size(),
+                        cudaMemcpyHostToDevice, stream), "upload schedule");
+  check(cudaMemcpyAsync(base + off_units, plan.units.data(), sizeof(WorkUnit) * plan.units.size(),
+                        cudaMemcpyHostToDevice, stream), "upload units");
+
+  TcParams p{};
+  p.rows[0] = l.rows; p.rows[1] = h.rows;
+  p.tiles[0] = (l.rows + kTileRows - 1) / kTileRows; p.tiles[1] = (h.rows + kTileRows - 1) / kTileRows;
+  p.sfa[0] = static_cast<const uint8_t*>(l.weight_scales); p.sfa[1] = static_cast<const uint8_t*>(h.weight_scales);
+  p.ids[0] = static_cast<const int32_t*>(l.ids); p.ids[1] = static_cast<const int32_t*>(h.ids);
+  p.sfb = static_cast<const uint8_t*>(any.activation_scales);
+  p.out = static_cast<uint16_t*>(any.output);
+  p.outputs = any.outputs; p.tokens = any.tokens; p.k = any.k; p.kblocks = any.k / kTileK;
+  p.n_tile = plan.n_tile; p.stages = plan.stages; p.dtype = dtype; p.tmem_cols = uint32_t(plan.tmem_cols);
+  p.issuers = plan.issuers;
+  p.weight_low = static_cast<const uint8_t*>(l.weight);
+  p.status = reinterpret_cast<int*>(base + off_status);
+  p.counters = reinterpret_cast<int*>(base + off_counters);
+  p.cta_begin = reinterpret_cast<const int*>(base + off_cta);
+  p.units = reinterpret_cast<const WorkUnit*>(base + off_units);
+  p.workspace = reinterpret_cast<float*>(base + off_work);
+  const CUtensorMap map_act = make_map(any.activation, any.tokens, any.k, plan.n_tile);
+  const CUtensorMap map_high = h.rows ? make_map(h.weight, h.rows, h.k, kTileRows) : map_act;
+  if (dtype == HG_DTYPE_BF16)
+    hybrid_gemm_tc_kernel<__nv_bfloat16><<<plan.grid, kTcThreads, plan.smem_bytes, stream>>>(p, map_high, map_act);
+  else
+    hybrid_gemm_tc_kernel<__half><<<plan.grid, kTcThreads, plan.smem_bytes, stream>>>(p, map_high, map_act);
+  check(cudaGetLastError(), "hybrid GEMM launch (static scratch)");
+}
+
 }  // namespace hg
+
+extern "C" int hg_run_static(int schedule, const hg_problem* low, const hg_problem* high, void* stream, int dtype) {
+  HG_TRY
+  if (!low || !high) throw std::runtime_error("Null argument to hg_run_static");
+  hg::tc_run_static(schedule, *low, *high, dtype, static_cast<cudaStream_t>(stream));
+  HG_CATCH
+}

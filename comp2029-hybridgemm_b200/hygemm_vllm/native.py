@@ -68,6 +68,7 @@ def library():
     lib.hg_status.argtypes = [vp, vp, C.POINTER(ci)]
     lib.hg_destroy.argtypes, lib.hg_destroy.restype = [vp], None
     lib.hg_plan.argtypes = [ci] * 6 + [C.POINTER(ci), C.POINTER(ci), ci]
+    lib.hg_run_static.argtypes = [ci, pp, pp, vp, ci]
     lib.hg_fused_error.restype = C.c_char_p
     lib.hg_fused_create.argtypes = [ci, pp, pp, vp, C.POINTER(vp)]
     lib.hg_fused_create_dtype.argtypes = [ci, pp, pp, vp, ci, C.POINTER(vp)]

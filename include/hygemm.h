@@ -112,6 +112,24 @@ int hg_status(void* handle, void* stream, int* status);
 int hg_plan(int rows_low, int rows_high, int tokens, int k, int sms, int schedule, int* header, int* units,
             int max_units);
 
+/* Bytes of the fixed scratch array behind hg_run_static (held on every GPU that loads the library). */
+#define HG_STATIC_SCRATCH_BYTES (8u << 20)
+
+/* The hybrid GEMM of hg_create + hg_run in one call that allocates no device memory (no counterpart in
+ * the reference, whose handles always own a workspace).  It is for callers that cannot call cudaMalloc
+ * where a layer runs: an engine whose memory pool owns the whole device, a latency-critical loop that
+ * cannot afford the device-wide synchronisation an allocation implies, or code that meets a shape only
+ * when it has to run it and so cannot warm a handle.  The tile schedule, split-K partial sums, arrival
+ * counters and status words live in one array of HG_STATIC_SCRATCH_BYTES inside the library image.
+ *   - `schedule` is an HG_SCHEDULE_* id 0..3, `dtype` an HG_DTYPE_*; inputs and outputs as for hg_run.
+ *   - The first call on a device looks up the array's device address and raises the kernel's
+ *     shared-memory limit: make that call before any stream capture.
+ *   - Every call uses the same array.  Calls on one stream are safe; calls that overlap on the GPU
+ *     (different streams or threads) race.  Counters and status are cleared at the start of each call.
+ *   - A shape whose schedule and partial sums exceed the array returns -1 with a message naming both
+ *     sizes; nothing is launched.  Use hg_create/hg_run for such shapes. */
+int hg_run_static(int schedule, const hg_problem* low, const hg_problem* high, void* stream, int dtype);
+
 /* Single-kernel path kept for binding compatibility
  * (integrations/vllm/native/fused_probe.cu:7-28).  The tcgen05 kernel already
  * covers both partitions in one launch, so these wrap the same implementation
