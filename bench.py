@@ -486,6 +486,7 @@ def main():
 
     # ---- per-launch GEMM durations in the same weight-cycling sequence: CUDA events recorded INSIDE a graph
     # of the step (event-record nodes on the launch stream), so the host launch path is not in the number.
+    timed_graph = None
     per, how = {}, "event-record nodes around each GEMM inside a CUDA graph of the step, 5 replays"
     try:
         if graph is None:
@@ -562,7 +563,17 @@ def main():
             line["cpu_baseline"], _ = cpu_reference_sample(min_seconds=10.0)
         print(json.dumps(line))
     if world > 1:
+        # Graphs that captured NCCL kernels must go before the communicator; a watchdog ends the process
+        # if the communicator teardown does not return (the result line is already printed and flushed).
+        sys.stdout.flush()
+        graph = timed_graph = None  # noqa: F841
+        torch.cuda.synchronize()
+        watchdog = threading.Timer(30.0, os._exit, args=(0,))
+        watchdog.daemon = True
+        watchdog.start()
+        dist.barrier()
         dist.destroy_process_group()
+        watchdog.cancel()
 
 
 if __name__ == "__main__":
