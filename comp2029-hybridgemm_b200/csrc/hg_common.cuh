@@ -6,6 +6,7 @@
 #include <cstdint>
 #include <stdexcept>
 #include <string>
+#include <utility>
 
 #include "../../include/hygemm.h"
 
@@ -39,6 +40,32 @@ __host__ __device__ inline int64_t scale_word_offset(int row, int kb, int k) {
 }
 
 #ifdef __CUDACC__
+// Programmatic dependent launch.  Every kernel of the library is launched with the
+// programmatic-stream-serialization attribute (unless HYGEMM_PDL=0): it may start while its
+// predecessor in the stream drains, does its set-up and any work that does not depend on the
+// predecessor, and calls pdl_wait() before it reads the predecessor's output or writes global memory.
+// pdl_trigger() lets the next kernel in the stream do the same.  Without the attribute both are no-ops.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+bool pdl_enabled();
+
+template <typename... KernelArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args&&... args) {
+  cudaLaunchConfig_t config{};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, KernelArgs(std::forward<Args>(args))...);
+}
+
 // Smallest e with amax * 2^-e <= MAX (448 for E4M3, 6 for E2M1), clamped to
 // [-127,127]; e = 0 for an all-zero block.  Equals ceil(log2(amax/MAX)) of
 // integrations/vllm/native/runtime.cu:71-72 for every 16-bit input (proved

@@ -62,6 +62,8 @@ struct SimtParams {
 template <typename T, int NT>
 __global__ void __launch_bounds__(128)
 simt_pair_kernel(SimtParams p) {
+  pdl_trigger();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int vrow = blockIdx.x * 4 + (threadIdx.x >> 5);
   if (vrow >= p.rows[0] + p.rows[1]) return;

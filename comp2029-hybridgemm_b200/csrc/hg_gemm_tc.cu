@@ -59,6 +59,7 @@ struct TcParams {
   int outputs, tokens, k, kblocks;
   int n_tile, stages, dtype;
   int issuers;    // MMA-issuing threads = independent accumulators per unit (1, 2 or 4)
+  int acc_slots;  // accumulator buffers: 2 lets the epilogue of a unit overlap the next main loop
   const uint8_t* weight_low;
   uint32_t tmem_cols;
   const WorkUnit* units;
@@ -232,6 +233,7 @@ template <typename T>
 __global__ void __launch_bounds__(kTcThreads, 1)
 hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant__ CUtensorMap map_high,
                       const __grid_constant__ CUtensorMap map_act) {
+  pdl_trigger();  // the next kernel in the stream may start its own set-up
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -279,11 +281,11 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = uint32_t(*tmem_slot);
 
-  // TMEM columns: two accumulator slots of issuers x acc_cols columns, then per issuer kScaleSets sets
-  // of (SFA, SFB), 4 columns each.
+  // TMEM columns: acc_slots accumulator slots of issuers x acc_cols columns, then per issuer kScaleSets
+  // sets of (SFA, SFB), 4 columns each.
   const uint32_t acc_cols = uint32_t((p.n_tile + 31) & ~31);
   const uint32_t acc_stride = acc_cols * uint32_t(p.issuers);
-  const uint32_t sf_cols = tmem_base + 2 * acc_stride;
+  const uint32_t sf_cols = tmem_base + uint32_t(p.acc_slots) * acc_stride;
 
   const int unit_begin = p.cta_begin[blockIdx.x], unit_end = p.cta_begin[blockIdx.x + 1];
   int error = 0;
@@ -295,6 +297,9 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
+      // Activations and their scales come from the previous kernel; the MXFP4 weight stream of the loader
+      // warps does not and is already running.
+      pdl_wait();
       for (int u = unit_begin; u < unit_end && !error; ++u) {
         const WorkUnit wu = p.units[u];
         const int part = wu.tile >= p.tiles[0];
@@ -379,9 +384,9 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
       for (int u = unit_begin; u < unit_end && !error; ++u, ++acc_it) {
         const WorkUnit wu = p.units[u];
         const int part = wu.tile >= p.tiles[0];
-        const int slot = acc_it & 1;
+        const int slot = acc_it % p.acc_slots;
         const uint32_t unit_stages = uint32_t(wu.kb_end - wu.kb_begin + 1) >> 1;
-        if (!mbar_wait(acc_empty_bar(slot), (uint32_t(acc_it >> 1) & 1u) ^ 1u, abort_flag)) { error = kErrMmaAcc; break; }
+        if (!mbar_wait(acc_empty_bar(slot), (uint32_t(acc_it / p.acc_slots) & 1u) ^ 1u, abort_flag)) { error = kErrMmaAcc; break; }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + uint32_t(slot) * acc_stride + uint32_t(q) * acc_cols;
         const uint32_t idesc = instr_desc(part == 0, p.n_tile);
@@ -433,15 +438,16 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
     const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
     int acc_it = 0, stored = 0;
     uint32_t ring = 0;
+    pdl_wait();  // nothing is written to global memory before every earlier kernel has finished
     for (int u = unit_begin; u < unit_end; ++u, ++acc_it) {
       const WorkUnit wu = p.units[u];
       const int part = wu.tile >= p.tiles[0];
       const int tile = part ? wu.tile - p.tiles[0] : wu.tile;
-      const int slot = acc_it & 1;
+      const int slot = acc_it % p.acc_slots;
       const int row = tile * kTileRows + row_in_tile;
       const bool row_ok = row < p.rows[part];
       const int channel = row_ok ? p.ids[part][row] : 0;   // fetched while the main loop runs
-      const bool ok = mbar_wait(acc_full_bar(slot), uint32_t(acc_it >> 1) & 1u, abort_flag);
+      const bool ok = mbar_wait(acc_full_bar(slot), uint32_t(acc_it / p.acc_slots) & 1u, abort_flag);
       if (!epilogue_all(ok)) { error = kErrEpilogue; break; }
       tc_fence_after();
       const int token0 = wu.token_tile * p.n_tile;
@@ -552,15 +558,18 @@ Plan make_plan(int rows_low, int rows_high, int tokens, int k, int sms, int sche
   if (const char* cap = std::getenv("HYGEMM_TC_STAGES"))  // tuning aid: cap the pipeline depth
     plan.stages = std::max(2, std::min(plan.stages, std::atoi(cap)));
   plan.smem_bytes = 1024 + plan.stages * stage_bytes + kBarrierBytes;
-  // MMA-issuing threads: two wherever TMEM holds two double-buffered accumulators per slot (512 columns
-  // in all); the pipeline depth is kept a multiple of the issuer count (see the kernel).
+  // MMA-issuing threads: two up to n_tile = 64, where TMEM (512 columns) holds two double-buffered
+  // accumulators per issuer.  At n_tile = 128 a second issuer would force single-buffered accumulators
+  // and a two-stage ring, which measured slower (gate_up M=128: 40.5 vs 34.3 us), so one issuer there.
+  // The pipeline depth is kept a multiple of the issuer count (see the kernel).
   plan.issuers = plan.n_tile <= 64 ? 2 : 1;
   if (const char* cap = std::getenv("HYGEMM_TC_ISSUERS"))  // tuning aid: 1, 2 or 4
-    plan.issuers = std::max(1, std::min(plan.n_tile <= 32 ? 4 : plan.issuers, std::atoi(cap)));
+    plan.issuers = std::max(1, std::min(plan.n_tile <= 32 ? 4 : plan.n_tile <= 64 ? 2 : 2, std::atoi(cap)));
   if (plan.issuers == 3) plan.issuers = 2;
+  plan.acc_slots = plan.issuers * 2 * round_up(plan.n_tile, 32) + plan.issuers * 8 * kScaleSets <= 512 ? 2 : 1;
   plan.stages = std::max(plan.issuers, plan.stages / plan.issuers * plan.issuers);
   plan.smem_bytes = 1024 + plan.stages * stage_bytes + kBarrierBytes;
-  int cols = plan.issuers * (2 * round_up(plan.n_tile, 32) + 8 * kScaleSets), pow2 = 32;
+  int cols = plan.issuers * (plan.acc_slots * round_up(plan.n_tile, 32) + 8 * kScaleSets), pow2 = 32;
   while (pow2 < cols) pow2 *= 2;
   plan.tmem_cols = pow2;
 
@@ -813,6 +822,7 @@ void tc_run(TcGemm* g, const hg_problem& l, const hg_problem& h, cudaStream_t st
   p.outputs = any.outputs; p.tokens = any.tokens; p.k = any.k; p.kblocks = any.k / kTileK;
   p.n_tile = plan.n_tile; p.stages = plan.stages; p.dtype = g->dtype; p.tmem_cols = uint32_t(plan.tmem_cols);
   p.issuers = plan.issuers;
+  p.acc_slots = plan.acc_slots;
   p.weight_low = static_cast<const uint8_t*>(l.weight);
   p.units = g->d_units; p.cta_begin = g->d_cta_begin;
   p.workspace = g->d_workspace; p.counters = g->d_counters; p.status = g->d_status;
@@ -820,10 +830,9 @@ void tc_run(TcGemm* g, const hg_problem& l, const hg_problem& h, cudaStream_t st
   const CUtensorMap map_act = make_map(any.activation, any.tokens, any.k, plan.n_tile);
   const CUtensorMap map_high = h.rows ? make_map(h.weight, h.rows, h.k, kTileRows) : map_act;
   if (g->dtype == HG_DTYPE_BF16)
-    hybrid_gemm_tc_kernel<__nv_bfloat16><<<plan.grid, kTcThreads, plan.smem_bytes, stream>>>(p, map_high, map_act);
+    check(launch_kernel(hybrid_gemm_tc_kernel<__nv_bfloat16>, dim3(plan.grid), dim3(kTcThreads), plan.smem_bytes, stream, p, map_high, map_act), "hybrid GEMM launch");
   else
-    hybrid_gemm_tc_kernel<__half><<<plan.grid, kTcThreads, plan.smem_bytes, stream>>>(p, map_high, map_act);
-  check(cudaGetLastError(), "hybrid GEMM launch");
+    check(launch_kernel(hybrid_gemm_tc_kernel<__half>, dim3(plan.grid), dim3(kTcThreads), plan.smem_bytes, stream, p, map_high, map_act), "hybrid GEMM launch");
 }
 
 void tc_destroy(TcGemm* g) {
@@ -947,6 +956,7 @@ void tc_run_static(int schedule, const hg_problem& l, const hg_problem& h, int d
   p.outputs = any.outputs; p.tokens = any.tokens; p.k = any.k; p.kblocks = any.k / kTileK;
   p.n_tile = plan.n_tile; p.stages = plan.stages; p.dtype = dtype; p.tmem_cols = uint32_t(plan.tmem_cols);
   p.issuers = plan.issuers;
+  p.acc_slots = plan.acc_slots;
   p.weight_low = static_cast<const uint8_t*>(l.weight);
   p.status = reinterpret_cast<int*>(base + off_status);
   p.counters = reinterpret_cast<int*>(base + off_counters);

@@ -31,6 +31,7 @@ struct Plan {
   int smem_bytes = 0;
   int tmem_cols = 0;
   int issuers = 1;         // MMA-issuing threads, each with its own TMEM accumulator
+  int acc_slots = 2;       // accumulator buffers per issuer
   int ws_slots = 0;        // fp32 [n_tile][128] slots
   int counters = 0;
   std::vector<WorkUnit> units;

@@ -9,6 +9,8 @@
 // word of the 512-byte scale atom.  Threads past the real work write the 0x7f
 // padding words of the last 128-row scale block, so no memset node precedes
 // the kernel and every byte of the scale buffer is rewritten on every call.
+#include <cstdlib>
+
 #include "hg_common.cuh"
 
 namespace hg {
@@ -18,10 +20,20 @@ std::string& last_error() {
   return message;
 }
 
+bool pdl_enabled() {
+  static const bool enabled = [] {
+    const char* v = std::getenv("HYGEMM_PDL");
+    return !(v && v[0] == '0');
+  }();
+  return enabled;
+}
+
 template <typename T, bool FP4, bool SILU, int MATH>
 __global__ void __launch_bounds__(256)
 mx_quant_kernel(const uint16_t* __restrict__ in, uint8_t* __restrict__ out, uint8_t* __restrict__ sf,
                 uint16_t* __restrict__ debug, int rows, int k) {
+  pdl_trigger();
+  pdl_wait();   // the input is usually the previous kernel's output
   const int kblocks = k >> 7;
   const int64_t real = int64_t(rows) * kblocks * 16;
   const int64_t tid = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -103,10 +115,9 @@ static cudaError_t launch_quant(const void* in, void* out, void* sf, void* debug
   const int64_t pad_rows = ((rows + 127) & ~127) - rows;
   const int64_t threads = int64_t(rows) * kblocks * 16 + pad_rows * kblocks;
   const int64_t blocks = (threads + 255) / 256;
-  mx_quant_kernel<T, FP4, SILU, MATH><<<unsigned(blocks), 256, 0, s>>>(
-      static_cast<const uint16_t*>(in), static_cast<uint8_t*>(out), static_cast<uint8_t*>(sf),
-      static_cast<uint16_t*>(debug), rows, k);
-  return cudaGetLastError();
+  return launch_kernel(mx_quant_kernel<T, FP4, SILU, MATH>, dim3(unsigned(blocks)), dim3(256), 0, s,
+                       static_cast<const uint16_t*>(in), static_cast<uint8_t*>(out), static_cast<uint8_t*>(sf),
+                       static_cast<uint16_t*>(debug), rows, k);
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
