@@ -253,6 +253,11 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+  // The schedule of this CTA is fetched before the set-up barrier so its latency overlaps the set-up.
+  const int unit_begin = p.cta_begin[blockIdx.x], unit_end = p.cta_begin[blockIdx.x + 1];
+  WorkUnit first_unit{};
+  if (unit_begin < unit_end) first_unit = p.units[unit_begin];
+
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_high)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_act)) : "memory");
@@ -287,7 +292,6 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
   const uint32_t acc_stride = acc_cols * uint32_t(p.issuers);
   const uint32_t sf_cols = tmem_base + uint32_t(p.acc_slots) * acc_stride;
 
-  const int unit_begin = p.cta_begin[blockIdx.x], unit_end = p.cta_begin[blockIdx.x + 1];
   int error = 0;
 
   if (warp == 0) {
@@ -301,7 +305,7 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
       // warps does not and is already running.
       pdl_wait();
       for (int u = unit_begin; u < unit_end && !error; ++u) {
-        const WorkUnit wu = p.units[u];
+        const WorkUnit wu = u == unit_begin ? first_unit : p.units[u];
         const int part = wu.tile >= p.tiles[0];
         const int tile = part ? wu.tile - p.tiles[0] : wu.tile;
         const int token0 = wu.token_tile * p.n_tile;
@@ -342,7 +346,7 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
     int stage = 0;
     uint32_t phase = 0;
     for (int u = unit_begin; u < unit_end && !error; ++u) {
-      const WorkUnit wu = p.units[u];
+      const WorkUnit wu = u == unit_begin ? first_unit : p.units[u];
       const int part = wu.tile >= p.tiles[0];
       const int row0 = wu.tile * kTileRows + rsub;  // first row of this thread (low partition only)
       const uint8_t* src0 = p.weight_low + int64_t(row0) * pitch + m * 8;
@@ -382,7 +386,7 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
       const uint32_t sf_base = sf_cols + uint32_t(q) * (8u * kScaleSets);
       uint32_t sf_flip = 0;
       for (int u = unit_begin; u < unit_end && !error; ++u, ++acc_it) {
-        const WorkUnit wu = p.units[u];
+        const WorkUnit wu = u == unit_begin ? first_unit : p.units[u];
         const int part = wu.tile >= p.tiles[0];
         const int slot = acc_it % p.acc_slots;
         const uint32_t unit_stages = uint32_t(wu.kb_end - wu.kb_begin + 1) >> 1;
@@ -440,7 +444,7 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
     uint32_t ring = 0;
     pdl_wait();  // nothing is written to global memory before every earlier kernel has finished
     for (int u = unit_begin; u < unit_end; ++u, ++acc_it) {
-      const WorkUnit wu = p.units[u];
+      const WorkUnit wu = u == unit_begin ? first_unit : p.units[u];
       const int part = wu.tile >= p.tiles[0];
       const int tile = part ? wu.tile - p.tiles[0] : wu.tile;
       const int slot = acc_it % p.acc_slots;

@@ -87,7 +87,8 @@ def check(status: int) -> None:
 
 
 def scale_size(rows: int, k: int) -> int:
-    return int(library().hg_scale_size(rows, k))
+    """Bytes of the padded scale buffer; the closed form of `hg_scale_size` (no foreign call on the hot path)."""
+    return ((rows + 127) // 128) * (k // 128) * 512 if rows > 0 and k > 0 else 0
 
 
 def _stream(device) -> int:
@@ -147,6 +148,7 @@ class DualLinear:
         self.calls = {}
         self.plans = plans
         self.plans_used = {}
+        self._problems = {}
 
     def __call__(self, x):
         if x.ndim != 2 or x.shape[1] != self.k or x.device != self.w4.device:
@@ -155,12 +157,26 @@ class DualLinear:
         return self.run_packed(q, sf)
 
     def problems(self, q, sf, y):
+        """The two `Problem` structs of a call (shared activation, scales and output pointers)."""
         tokens = q.shape[0]
         low = Problem(self.lo.numel(), tokens, self.k, self.outputs, self.w4.data_ptr(), q.data_ptr(),
                       self.sf4.data_ptr(), sf.data_ptr(), self.lo.data_ptr(), y.data_ptr())
         high = Problem(self.hi.numel(), tokens, self.k, self.outputs, self.w8.data_ptr(), q.data_ptr(),
                        self.sf8.data_ptr(), sf.data_ptr(), self.hi.data_ptr(), y.data_ptr())
         return low, high
+
+    def _rebound(self, tokens, q, sf, y):
+        """Per-token-count `Problem` pair kept between calls; only the three per-call pointers change."""
+        pair = self._problems.get(tokens)
+        if pair is None or pair[2] != (self.w4.data_ptr(), self.sf4.data_ptr()):
+            low, high = self.problems(q, sf, y)
+            pair = self._problems[tokens] = (low, high, (self.w4.data_ptr(), self.sf4.data_ptr()),
+                                             C.byref(low), C.byref(high))
+            return pair
+        qp, sp, yp = q.data_ptr(), sf.data_ptr(), y.data_ptr()
+        for prob in pair[:2]:
+            prob.activation, prob.activation_scales, prob.output = qp, sp, yp
+        return pair
 
     def run_packed(self, q, sf):
         """GEMM on already-quantised activations (reference: native.py:75-107)."""
@@ -175,7 +191,7 @@ class DualLinear:
         y = torch.empty((tokens, self.outputs), dtype=self.dtype, device=q.device)
         if tokens == 0:
             return y
-        low, high = self.problems(q, sf, y)
+        low, high, _, low_ref, high_ref = self._rebound(tokens, q, sf, y)
         stream = _stream(q.device)
         low_id, high_id, policy = self.low_id, self.high_id, int(self.concurrent)
         if self.plans:
@@ -188,10 +204,12 @@ class DualLinear:
             if torch.cuda.is_current_stream_capturing():
                 raise RuntimeError(f"HyGEMM shape T={key} must be warmed before graph capture")
             handle = C.c_void_p()
-            check(library().hg_create_dtype(low_id, high_id, C.byref(low), C.byref(high), stream,
+            check(library().hg_create_dtype(low_id, high_id, low_ref, high_ref, stream,
                                             DTYPES[self.dtype], C.byref(handle)))
             self.handles[key] = handle
-        check(library().hg_run(handle, C.byref(low), C.byref(high), stream, policy))
+        status = _lib.hg_run(handle, low_ref, high_ref, stream, policy)
+        if status:
+            check(status)
         self.calls[tokens] = self.calls.get(tokens, 0) + 1
         return y
 
