@@ -152,6 +152,17 @@ def build_layer(device, layer_seed: int, rank: int, world: int):
     return layer
 
 
+def launches_of(rt, tokens):
+    """Kernels one hybrid GEMM call launches: 1, or 2 when its cut tiles are summed by the reduce kernel."""
+    import ctypes as C
+    from hygemm_vllm import native
+    header = (C.c_int * 12)()
+    props = torch.cuda.get_device_properties(rt.w4.device)
+    native.check(native.library().hg_plan(int(rt.lo.numel()), int(rt.hi.numel()), tokens, rt.k,
+                                          props.multi_processor_count, rt.low_id, header, None, 0))
+    return 1 + header[10]
+
+
 def shard_stats(layer):
     """(K, N, H) of each GEMM as this rank runs it."""
     return {name: (rt.k, rt.outputs, int(rt.hi.numel())) for name, rt in layer.items()}
@@ -175,7 +186,10 @@ class Sweep:
             self.host[m] = {"x_qkv": x[0].contiguous().pin_memory(), "x_gate": x[2].contiguous().pin_memory(),
                             "x_o": x[1][:, :k_o].contiguous().pin_memory()}
             self.dev[m] = {n: t.to(device) for n, t in self.host[m].items()}
-        self.launches_per_step = 8 * len(M_SWEEP)
+        # 4 quantiser launches per M plus the GEMM launches (a GEMM whose cut tiles are summed by the separate
+        # reduce kernel counts two)
+        self.launches_per_step = sum(4 + sum(launches_of(self.layer_for(i)[name], m) for name in SHAPES)
+                                     for i, m in enumerate(M_SWEEP))
         self.event_factory = lambda: torch.cuda.Event(enable_timing=True)
 
     def layer_for(self, i):

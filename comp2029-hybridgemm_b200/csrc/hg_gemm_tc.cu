@@ -60,6 +60,7 @@ struct TcParams {
   int n_tile, stages, dtype;
   int issuers;    // MMA-issuing threads = independent accumulators per unit (1, 2 or 4)
   int acc_slots;  // accumulator buffers: 2 lets the epilogue of a unit overlap the next main loop
+  int external_reduce;  // cut tiles only store partial sums; splitk_reduce_kernel adds them
   const uint8_t* weight_low;
   uint32_t tmem_cols;
   const WorkUnit* units;
@@ -493,7 +494,7 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty_bar(slot));
 
-      if (wu.nsplit > 1) {
+      if (wu.nsplit > 1 && !p.external_reduce) {
         // Deterministic split-K fix-up: the last unit of the tile to arrive sums
         // all partials in K order.  No unit ever waits for another.
         epilogue_sync();
@@ -542,6 +543,44 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols) : "memory");
   }
+}
+
+// Fixed-order sum of the partial tiles of every cut (tile, token tile) for wide token tiles
+// (the counterpart of the reference's reduce kernel, src/kernel/output_channel_gemv.cu:73-81).
+// One block per (cut tile, 8 token columns), one thread per weight row.
+struct ReduceParams {
+  int rows[2];
+  int tiles[2];
+  const int32_t* ids[2];
+  uint16_t* out;
+  int outputs, tokens, n_tile;
+  const float* workspace;
+  const int* cut_tiles;   // 4 ints each: tile, token_tile, ws_slot, nsplit
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kTileRows)
+splitk_reduce_kernel(const ReduceParams rp) {
+  pdl_trigger();
+  pdl_wait();  // the partial sums come from the GEMM launched just before
+  const int column_blocks = rp.n_tile >> 3;
+  const int cut = blockIdx.x / column_blocks, c0 = (blockIdx.x % column_blocks) * 8;
+  const int tile_v = rp.cut_tiles[4 * cut], token_tile = rp.cut_tiles[4 * cut + 1];
+  const int slot = rp.cut_tiles[4 * cut + 2], nsplit = rp.cut_tiles[4 * cut + 3];
+  const int part = tile_v >= rp.tiles[0];
+  const int row = (part ? tile_v - rp.tiles[0] : tile_v) * kTileRows + int(threadIdx.x);
+  if (row >= rp.rows[part]) return;
+  const int channel = rp.ids[part][row];
+  const int token0 = token_tile * rp.n_tile + c0;
+  const float* src = rp.workspace + int64_t(slot) * (int64_t(rp.n_tile) * kTileRows) + int64_t(c0) * kTileRows + threadIdx.x;
+  float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int s = 0; s < nsplit; ++s) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sum[i] += __ldcg(src + (int64_t(s) * rp.n_tile + i) * kTileRows);
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    if (token0 + i < rp.tokens) scatter_store<T>(rp.out, int64_t(token0 + i) * rp.outputs + channel, sum[i]);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -706,6 +745,21 @@ Plan make_plan(int rows_low, int rows_high, int tokens, int k, int sms, int sche
     throw std::runtime_error("Unknown tile schedule id");
   }
   plan.schedule = schedule;
+  // With wide token tiles the partial sums of a cut tile are large (n_tile x 128 fp32 per piece) and only
+  // one CTA per tile, the last to arrive, would sum them while the others sit idle: measured 68 us for
+  // down at M = 128.  From n_tile = 64 on, a second, fully parallel kernel does the fixed-order sum.
+  plan.external_reduce = plan.n_tile >= 64 && plan.ws_slots > 0;
+  plan.cut_tiles.clear();
+  if (plan.external_reduce) {
+    std::vector<char> seen(size_t(tiles) * plan.token_tiles, 0);
+    for (const WorkUnit& unit : plan.units) {
+      const size_t item = size_t(unit.tile) * plan.token_tiles + unit.token_tile;
+      if (unit.nsplit > 1 && !seen[item]) {
+        seen[item] = 1;
+        plan.cut_tiles.insert(plan.cut_tiles.end(), {unit.tile, unit.token_tile, unit.ws_slot, unit.nsplit});
+      }
+    }
+  }
   return plan;
 }
 
@@ -754,6 +808,7 @@ struct TcGemm {
   float* d_workspace = nullptr;
   int* d_counters = nullptr;
   int* d_status = nullptr;
+  int* d_cut = nullptr;
 };
 
 static void validate(const hg_problem& l, const hg_problem& h) {
@@ -800,6 +855,9 @@ TcGemm* tc_create(const hg_problem& l, const hg_problem& h, int schedule, int dt
   check(cudaMalloc(&g->d_workspace, sizeof(float) * std::max<int64_t>(1, int64_t(plan.ws_slots) * plan.n_tile * kTileRows)), "cudaMalloc workspace");
   check(cudaMalloc(&g->d_counters, sizeof(int) * std::max(1, plan.counters)), "cudaMalloc counters");
     check(cudaMalloc(&g->d_status, sizeof(int) * 4), "cudaMalloc status");
+  check(cudaMalloc(&g->d_cut, sizeof(int) * std::max<size_t>(4, plan.cut_tiles.size())), "cudaMalloc cut list");
+  if (!plan.cut_tiles.empty())
+    check(cudaMemcpyAsync(g->d_cut, plan.cut_tiles.data(), sizeof(int) * plan.cut_tiles.size(), cudaMemcpyHostToDevice, stream), "upload cut list");
   check(cudaMemcpyAsync(g->d_units, plan.units.data(), sizeof(WorkUnit) * plan.units.size(), cudaMemcpyHostToDevice, stream), "upload units");
   check(cudaMemcpyAsync(g->d_cta_begin, plan.cta_begin.data(), sizeof(int) * plan.cta_begin.size(), cudaMemcpyHostToDevice, stream), "upload schedule");
   check(cudaMemsetAsync(g->d_counters, 0, sizeof(int) * std::max(1, plan.counters), stream), "clear counters");
@@ -808,6 +866,26 @@ TcGemm* tc_create(const hg_problem& l, const hg_problem& h, int schedule, int dt
   if (dtype == HG_DTYPE_BF16) configure_kernel<__nv_bfloat16>();
   else configure_kernel<__half>();
   return g.release();
+}
+
+// Second launch of a call whose cut tiles are summed outside the GEMM kernel.
+static void launch_reduce(const Plan& plan, const TcParams& p, const int* cut_tiles, int dtype, cudaStream_t stream, bool pdl) {
+  if (!plan.external_reduce || plan.cut_tiles.empty()) return;
+  ReduceParams rp{};
+  rp.rows[0] = p.rows[0]; rp.rows[1] = p.rows[1];
+  rp.tiles[0] = p.tiles[0]; rp.tiles[1] = p.tiles[1];
+  rp.ids[0] = p.ids[0]; rp.ids[1] = p.ids[1];
+  rp.out = p.out; rp.outputs = p.outputs; rp.tokens = p.tokens; rp.n_tile = p.n_tile;
+  rp.workspace = p.workspace; rp.cut_tiles = cut_tiles;
+  const dim3 grid(unsigned(plan.cut_tiles.size() / 4 * size_t(plan.n_tile / 8))), block(kTileRows);
+  if (pdl) {
+    check(dtype == HG_DTYPE_BF16 ? launch_kernel(splitk_reduce_kernel<__nv_bfloat16>, grid, block, 0, stream, rp)
+                                 : launch_kernel(splitk_reduce_kernel<__half>, grid, block, 0, stream, rp), "split-K reduce launch");
+  } else {
+    if (dtype == HG_DTYPE_BF16) splitk_reduce_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>(rp);
+    else splitk_reduce_kernel<__half><<<grid, block, 0, stream>>>(rp);
+    check(cudaGetLastError(), "split-K reduce launch");
+  }
 }
 
 void tc_run(TcGemm* g, const hg_problem& l, const hg_problem& h, cudaStream_t stream) {
@@ -827,6 +905,7 @@ void tc_run(TcGemm* g, const hg_problem& l, const hg_problem& h, cudaStream_t st
   p.n_tile = plan.n_tile; p.stages = plan.stages; p.dtype = g->dtype; p.tmem_cols = uint32_t(plan.tmem_cols);
   p.issuers = plan.issuers;
   p.acc_slots = plan.acc_slots;
+  p.external_reduce = plan.external_reduce ? 1 : 0;
   p.weight_low = static_cast<const uint8_t*>(l.weight);
   p.units = g->d_units; p.cta_begin = g->d_cta_begin;
   p.workspace = g->d_workspace; p.counters = g->d_counters; p.status = g->d_status;
@@ -837,11 +916,12 @@ void tc_run(TcGemm* g, const hg_problem& l, const hg_problem& h, cudaStream_t st
     check(launch_kernel(hybrid_gemm_tc_kernel<__nv_bfloat16>, dim3(plan.grid), dim3(kTcThreads), plan.smem_bytes, stream, p, map_high, map_act), "hybrid GEMM launch");
   else
     check(launch_kernel(hybrid_gemm_tc_kernel<__half>, dim3(plan.grid), dim3(kTcThreads), plan.smem_bytes, stream, p, map_high, map_act), "hybrid GEMM launch");
+  launch_reduce(plan, p, g->d_cut, g->dtype, stream, true);
 }
 
 void tc_destroy(TcGemm* g) {
   if (!g) return;
-  cudaFree(g->d_units); cudaFree(g->d_cta_begin); cudaFree(g->d_workspace); cudaFree(g->d_counters); cudaFree(g->d_status);
+  cudaFree(g->d_units); cudaFree(g->d_cta_begin); cudaFree(g->d_workspace); cudaFree(g->d_counters); cudaFree(g->d_status); cudaFree(g->d_cut);
   delete g;
 }
 
@@ -932,12 +1012,13 @@ void tc_run_static(int schedule, const hg_problem& l, const hg_problem& h, int d
   }
   const Plan& plan = st.plan;
 
-  // Carve the array: status | counters | cta_begin | units | workspace.
+  // Carve the array: status | counters | cta_begin | units | cut list | workspace.
   const size_t off_status = 0;
   const size_t off_counters = 256;
   const size_t off_cta = align_up(off_counters + sizeof(int) * size_t(std::max(1, plan.counters)), 256);
   const size_t off_units = align_up(off_cta + sizeof(int) * plan.cta_begin.size(), 256);
-  const size_t off_work = align_up(off_units + sizeof(WorkUnit) * std::max<size_t>(1, plan.units.size()), 256);
+  const size_t off_cut = align_up(off_units + sizeof(WorkUnit) * std::max<size_t>(1, plan.units.size()), 256);
+  const size_t off_work = align_up(off_cut + sizeof(int) * std::max<size_t>(4, plan.cut_tiles.size()), 256);
   const size_t total = off_work + sizeof(float) * size_t(plan.ws_slots) * size_t(plan.n_tile) * kTileRows;
   if (total > size_t(HG_STATIC_SCRATCH_BYTES))
     throw std::runtime_error("hg_run_static: this shape needs " + std::to_string(total) +
@@ -949,6 +1030,9 @@ void tc_run_static(int schedule, const hg_problem& l, const hg_problem& h, int d
                         cudaMemcpyHostToDevice, stream), "upload schedule");
   check(cudaMemcpyAsync(base + off_units, plan.units.data(), sizeof(WorkUnit) * plan.units.size(),
                         cudaMemcpyHostToDevice, stream), "upload units");
+  if (!plan.cut_tiles.empty())
+    check(cudaMemcpyAsync(base + off_cut, plan.cut_tiles.data(), sizeof(int) * plan.cut_tiles.size(),
+                          cudaMemcpyHostToDevice, stream), "upload cut list");
 
   TcParams p{};
   p.rows[0] = l.rows; p.rows[1] = h.rows;
@@ -961,6 +1045,7 @@ void tc_run_static(int schedule, const hg_problem& l, const hg_problem& h, int d
   p.n_tile = plan.n_tile; p.stages = plan.stages; p.dtype = dtype; p.tmem_cols = uint32_t(plan.tmem_cols);
   p.issuers = plan.issuers;
   p.acc_slots = plan.acc_slots;
+  p.external_reduce = plan.external_reduce ? 1 : 0;
   p.weight_low = static_cast<const uint8_t*>(l.weight);
   p.status = reinterpret_cast<int*>(base + off_status);
   p.counters = reinterpret_cast<int*>(base + off_counters);
@@ -974,6 +1059,7 @@ void tc_run_static(int schedule, const hg_problem& l, const hg_problem& h, int d
   else
     hybrid_gemm_tc_kernel<__half><<<plan.grid, kTcThreads, plan.smem_bytes, stream>>>(p, map_high, map_act);
   check(cudaGetLastError(), "hybrid GEMM launch (static scratch)");
+  launch_reduce(plan, p, reinterpret_cast<const int*>(base + off_cut), dtype, stream, false);
 }
 
 }  // namespace hg

@@ -34,6 +34,8 @@ struct Plan {
   int acc_slots = 2;       // accumulator buffers per issuer
   int ws_slots = 0;        // fp32 [n_tile][128] slots
   int counters = 0;
+  bool external_reduce = false;  // cut tiles are summed by splitk_reduce_kernel instead of the last arriver
+  std::vector<int> cut_tiles;    // 4 ints per cut (tile, token tile): tile, token_tile, ws_slot, nsplit
   std::vector<WorkUnit> units;
   std::vector<int> cta_begin;  // grid + 1 offsets into units
 };

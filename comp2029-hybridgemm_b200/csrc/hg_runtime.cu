@@ -109,9 +109,10 @@ int hg_plan(int rows_low, int rows_high, int tokens, int k, int sms, int schedul
   if (!header || rows_low < 0 || rows_high < 0 || rows_low + rows_high == 0 || tokens <= 0 || k <= 0 || k % 128 || sms <= 0)
     throw std::runtime_error("Invalid hg_plan arguments");
   const hg::Plan plan = hg::make_plan(rows_low, rows_high, tokens, k, sms, schedule);
-  const int values[10] = {plan.schedule, plan.grid, plan.n_tile, plan.token_tiles, plan.stages, plan.smem_bytes,
-                          plan.tmem_cols, plan.ws_slots, plan.counters, int(plan.units.size())};
-  std::copy(values, values + 10, header);
+  const int values[12] = {plan.schedule, plan.grid, plan.n_tile, plan.token_tiles, plan.stages, plan.smem_bytes,
+                          plan.tmem_cols, plan.ws_slots, plan.counters, int(plan.units.size()),
+                          plan.external_reduce ? 1 : 0, plan.issuers};
+  std::copy(values, values + 12, header);
   if (units) {
     if (int(plan.units.size()) > max_units) throw std::runtime_error("hg_plan: unit buffer too small");
     for (int c = 0; c < plan.grid; ++c)

@@ -105,9 +105,9 @@ void hg_destroy(void* handle);
 int hg_status(void* handle, void* stream, int* status);
 /* Host-only view of the tile schedule hg_create would build for a shape on a
  * device with `sms` SMs (no GPU needed; no counterpart in the reference, whose
- * schedules live inside CUTLASS).  header[10] = schedule, grid, n_tile,
+ * schedules live inside CUTLASS).  header[12] = schedule, grid, n_tile,
  * token_tiles, stages, shared bytes, TMEM columns, workspace slots, counters,
- * units; units (optional) receives 9 ints per unit: cta, tile, token_tile,
+ * units, separate reduce launch (0/1), MMA-issuing threads; units (optional) receives 9 ints per unit: cta, tile, token_tile,
  * kb_begin, kb_end, split, nsplit, ws_slot, counter. */
 int hg_plan(int rows_low, int rows_high, int tokens, int k, int sms, int schedule, int* header, int* units,
             int max_units);

@@ -24,7 +24,7 @@ SCHEDULES = {"auto": 0, "data_parallel": 1, "split_k": 2, "stream_k": 3}
 def expected_work(case, schedule):
     """Closed-form totals the kernel's audit counters must reproduce."""
     lib = native.library()
-    header = (C.c_int * 10)()
+    header = (C.c_int * 12)()
     props = torch.cuda.get_device_properties(0)
     native.check(lib.hg_plan(case["lo"].size, case["hi"].size, case["tokens"], case["k"],
                              props.multi_processor_count, schedule, header, None, 0))

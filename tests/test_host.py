@@ -56,7 +56,7 @@ def test_scale_size_and_argument_errors_without_gpu():
 
 def plan(lo, hi, tokens, k, schedule=0, sms=148):
     lib = native.library()
-    header = (C.c_int * 10)()
+    header = (C.c_int * 12)()
     native.check(lib.hg_plan(lo, hi, tokens, k, sms, schedule, header, None, 0))
     units = (C.c_int * (9 * header[9]))()
     native.check(lib.hg_plan(lo, hi, tokens, k, sms, schedule, header, units, header[9]))
@@ -73,7 +73,8 @@ def test_every_schedule_covers_each_tile_and_k_block_exactly_once(schedule, toke
     for lo, hi, k in SHAPES:
         for sms in (148, 7):
             header, units = plan(lo, hi, tokens, k, schedule, sms)
-            sched, grid, n_tile, token_tiles, stages, smem, tmem, slots, counters, n_units = header
+            sched, grid, n_tile, token_tiles, stages, smem, tmem, slots, counters, n_units, reduce2, issuers = header
+            assert reduce2 == int(n_tile >= 64 and slots > 0) and stages % issuers == 0
             assert 1 <= grid <= sms and n_tile % 16 == 0 and 16 <= n_tile <= 128
             assert token_tiles == -(-tokens // n_tile) and (token_tiles == 1 or n_tile == 128)
             assert stages >= 2 and smem <= 232448 and tmem in (32, 64, 128, 256, 512)
