@@ -186,9 +186,11 @@ class Sweep:
             self.host[m] = {"x_qkv": x[0].contiguous().pin_memory(), "x_gate": x[2].contiguous().pin_memory(),
                             "x_o": x[1][:, :k_o].contiguous().pin_memory()}
             self.dev[m] = {n: t.to(device) for n, t in self.host[m].items()}
-        # 4 quantiser launches per M plus the GEMM launches (a GEMM whose cut tiles are summed by the separate
+        # quantiser launches per M (one SwiGLU-quantiser; three activation quantisers unless they are fused
+        # into the GEMM launch) plus the GEMM launches (a GEMM whose cut tiles are summed by the separate
         # reduce kernel counts two)
-        self.launches_per_step = sum(4 + sum(launches_of(self.layer_for(i)[name], m) for name in SHAPES)
+        fused = native.FUSED_QUANT_TOKENS
+        self.launches_per_step = sum((1 if m <= fused else 4) + sum(launches_of(self.layer_for(i)[name], m) for name in SHAPES)
                                      for i, m in enumerate(M_SWEEP))
         self.event_factory = lambda: torch.cuda.Event(enable_timing=True)
 
@@ -201,20 +203,30 @@ class Sweep:
         native, producer = self.native, self.producer
         out = {}
 
-        def gemm(name, q, sf):
+        def timed(name, call):
             if events is None:
-                return layer[name].run_packed(q, sf)
+                return call()
             a, b = self.event_factory(), self.event_factory()
             a.record()
-            y = layer[name].run_packed(q, sf)
+            y = call()
             b.record()
             events.append((name, m, a, b))
             return y
 
-        out["qkv"] = gemm("qkv", *native.pack(x["x_qkv"]))
-        y_o = gemm("o_proj", *native.pack(x["x_o"]))
-        gate_up = gemm("gate_up", *native.pack(x["x_gate"]))
-        y_d = gemm("down", *producer.silu_pack(gate_up, 0))
+        # What `layer(x)` (the plugin-facing call) does: up to 16 tokens the activations are quantised inside
+        # the GEMM launch (hg_run_x); above that the quantiser is its own launch.  Events bracket the GEMM launch.
+        def linear(name, xin):
+            rt = layer[name]
+            if m <= native.FUSED_QUANT_TOKENS:
+                return timed(name, lambda: rt(xin))
+            q, sf = native.pack(xin)
+            return timed(name, lambda: rt.run_packed(q, sf))
+
+        out["qkv"] = linear("qkv", x["x_qkv"])
+        y_o = linear("o_proj", x["x_o"])
+        gate_up = linear("gate_up", x["x_gate"])
+        q, sf = producer.silu_pack(gate_up, 0)
+        y_d = timed("down", lambda: layer["down"].run_packed(q, sf))
         if self.world > 1:
             torch.distributed.all_reduce(y_o, group=self.group)
             torch.distributed.all_reduce(y_d, group=self.group)
@@ -324,7 +336,8 @@ def run_single_gemm(args, device):
     schedule = int(fields[2]) if len(fields) > 2 else 0
     k, parts = SHAPES[name]
     n = sum(parts.values())
-    h = high_quota(n) if len(fields) < 4 else int(round(float(fields[3]) * n))
+    h = high_quota(n) if len(fields) < 4 or fields[3] == '' else int(round(float(fields[3]) * n))
+    fused = len(fields) > 4 and fields[4] == 'fused'
     weight_bytes = (n - h) * k // 2 + h * k
     copies = max(2, -(-300_000_000 // weight_bytes))            # > 2x the 126 MB L2 between reuses
     g = torch.Generator().manual_seed(SEED)
@@ -354,7 +367,10 @@ def run_single_gemm(args, device):
         stream = torch.cuda.current_stream().cuda_stream      # the capture stream while a graph is recorded
         for i in range(count):
             handle, low, hi = calls[i % copies]
-            native.check(lib.hg_run(handle, C.byref(low), C.byref(hi), stream, 0))
+            if fused:
+                native.check(lib.hg_run_x(handle, C.byref(low), C.byref(hi), x.data_ptr(), 1, stream))
+            else:
+                native.check(lib.hg_run(handle, C.byref(low), C.byref(hi), stream, 0))
 
     # `count` launches back to back (weight copies cycled) as one CUDA graph, so the host launch rate
     # does not bound what is measured; one event pair around each replay.
@@ -395,7 +411,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--gemm", default=None, metavar="NAME:M[:SCHEDULE[:HIGH_FRACTION]]",
+    ap.add_argument("--gemm", default=None, metavar="NAME:M[:SCHEDULE[:HIGH_FRACTION[:fused]]]",
                     help="profiling aid: run only this GEMM (e.g. gate_up:16) a few times on cold weights and exit")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
@@ -553,7 +569,8 @@ def main():
             "dtype": "mxfp4/mxfp8 x mxfp8 -> fp32 accumulate -> bf16", "data": "synthetic",
             "config": {"workload": "Qwen2.5-7B layer-shape hybrid GEMM sweep: qkv 3584->4608, o_proj 3584->3584, "
                                    "gate_up 3584->37888, down 18944->3584; M in 1,2,4,8,16,32,64,128; 10% MXFP8 channels",
-                       "step": "per M: quantise+qkv, quantise+o_proj, quantise+gate_up, SwiGLU-quantise+down",
+                       "step": "per M: quantise+qkv, quantise+o_proj, quantise+gate_up, SwiGLU-quantise+down "
+                               "(M<=16: the three activation quantisers run inside their GEMM launch)",
                        "parallelism": f"tp{world}" if world > 1 else "single GPU",
                        "l2": "inputs larger than L2: two weight sets (272 MB) alternate between consecutive M",
                        "launch": note, "seed": SEED},

@@ -62,6 +62,8 @@ struct TcParams {
   int acc_slots;  // accumulator buffers: 2 lets the epilogue of a unit overlap the next main loop
   int external_reduce;  // cut tiles only store partial sums; splitk_reduce_kernel adds them
   const uint8_t* weight_low;
+  const uint16_t* x;  // fused mode: 16-bit activations [tokens,k], quantised in the kernel (tokens <= 16); else null
+  int x_bf16;
   uint32_t tmem_cols;
   const WorkUnit* units;
   const int* cta_begin;
@@ -220,6 +222,7 @@ __host__ __device__ inline SmemLayout smem_layout(int stages, int n_tile) {
 constexpr int kScaleSets = 2;  // TMEM scale-factor buffers, alternated per K128 block
 constexpr int kBarrierBytes = (2 * kMaxStages + 5) * 8 + 32;
 constexpr int kLoaderThreads = 128;  // warps 6..9
+constexpr int kQuantThreads = 128;   // warps 13..16 (fused activation quantisation)
 
 // 8-byte asynchronous copy global -> shared; src_bytes = 0 writes zeros instead.
 __device__ __forceinline__ void cp_async_8(uint32_t dst, const void* src, uint32_t src_bytes) {
@@ -263,7 +266,8 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_high)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_act)) : "memory");
     for (int s = 0; s < p.stages; ++s) {
-      mbar_init(full_bar(s), 1 + kLoaderThreads);  // TMA thread (with the byte count) + every loader thread
+      // TMA thread (with the byte count) + every loader thread (+ every quantiser thread in fused mode)
+      mbar_init(full_bar(s), 1 + kLoaderThreads + (p.x ? kQuantThreads : 0));
       mbar_init(empty_bar(s), 1);                  // released by the MMA thread's commit
     }
     for (int s = 0; s < 2; ++s) {
@@ -303,8 +307,8 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       // Activations and their scales come from the previous kernel; the MXFP4 weight stream of the loader
-      // warps does not and is already running.
-      pdl_wait();
+      // warps does not and is already running.  (Fused mode: this thread only moves weights and their scales.)
+      if (!p.x) pdl_wait();
       for (int u = unit_begin; u < unit_end && !error; ++u) {
         const WorkUnit wu = u == unit_begin ? first_unit : p.units[u];
         const int part = wu.tile >= p.tiles[0];
@@ -316,16 +320,19 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
           const int nkb = min(2, wu.kb_end - kb);
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { error = kErrProducer; break; }
           const uint32_t bar = full_bar(stage);
-          mbar_expect_tx(bar, uint32_t(nkb) * ((part ? 16384u : 0u) + lay.b_tile + 1024u));
+          const bool fused = p.x != nullptr;  // activations and their scales are then produced by the loader warps
+          mbar_expect_tx(bar, uint32_t(nkb) * ((part ? 16384u : 0u) + (fused ? 512u : lay.b_tile + 1024u)));
           for (int i = 0; i < nkb; ++i) {
             if (part)
               tma_load_2d(base + lay.a + uint32_t(stage) * 32768u + uint32_t(i) * 16384u, &map_high, bar,
                           (kb + i) * kTileK, tile * kTileRows);
-            tma_load_2d(base + lay.b + (uint32_t(stage) * 2u + uint32_t(i)) * lay.b_tile, &map_act, bar,
-                        (kb + i) * kTileK, token0);
+            if (!fused)
+              tma_load_2d(base + lay.b + (uint32_t(stage) * 2u + uint32_t(i)) * lay.b_tile, &map_act, bar,
+                          (kb + i) * kTileK, token0);
           }
           bulk_load(base + lay.sfa + uint32_t(stage) * 1024u, sfa_src + int64_t(kb) * 512, uint32_t(nkb) * 512u, bar);
-          bulk_load(base + lay.sfb + uint32_t(stage) * 1024u, sfb_src + int64_t(kb) * 512, uint32_t(nkb) * 512u, bar);
+          if (!fused)
+            bulk_load(base + lay.sfb + uint32_t(stage) * 1024u, sfb_src + int64_t(kb) * 512, uint32_t(nkb) * 512u, bar);
           if (++stage == p.stages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -346,33 +353,122 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
     const int64_t pitch = p.k >> 1;  // bytes per packed row
     int stage = 0;
     uint32_t phase = 0;
-    for (int u = unit_begin; u < unit_end && !error; ++u) {
-      const WorkUnit wu = u == unit_begin ? first_unit : p.units[u];
+    int u = unit_begin;
+    WorkUnit wu = first_unit;
+    int kb = wu.kb_begin;
+    while (u < unit_end && !error) {
       const int part = wu.tile >= p.tiles[0];
-      const int row0 = wu.tile * kTileRows + rsub;  // first row of this thread (low partition only)
-      const uint8_t* src0 = p.weight_low + int64_t(row0) * pitch + m * 8;
-      for (int kb = wu.kb_begin; kb < wu.kb_end; kb += 2) {
+      const int nkb = min(2, wu.kb_end - kb);
+      bool ok = true;
+      if (lane == 0) ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag);
+      ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;
+      if (!ok) { error = kErrLoader; break; }
+      if (!part && blk < nkb) {
+        const int row0 = wu.tile * kTileRows + rsub;  // first row of this thread (low partition only)
+        const uint8_t* src = p.weight_low + int64_t(row0) * pitch + m * 8 + int64_t(kb) * 64;
+        const uint32_t dst = base + lay.a + uint32_t(stage) * 32768u + dst_off;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const bool valid = row0 + 8 * i < p.rows[0];
+          cp_async_8(dst + uint32_t(i) * 1024u, valid ? src + int64_t(8 * i) * pitch : p.weight_low, valid ? 8u : 0u);
+        }
+      }
+      // Position of the next stage (next K256 of this unit, or the start of the next unit).
+      int next_u = u, next_kb = kb + 2;
+      WorkUnit next_wu = wu;
+      if (next_kb >= wu.kb_end) {
+        ++next_u;
+        if (next_u < unit_end) { next_wu = p.units[next_u]; next_kb = next_wu.kb_begin; }
+      }
+      cp_async_arrive(full_bar(stage));
+      if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+      u = next_u; wu = next_wu; kb = next_kb;
+    }
+    // Copies still in flight must land before shared memory is released.
+    asm volatile("cp.async.wait_all;" ::: "memory");
+  } else if (warp >= 13) {
+    // ------------------------------------------------------------------ activation quantisers (warps 13..16)
+    // Fused mode only (decode, at most 16 tokens; p.x != null).  Thread tq owns one K32 group (tq % 8) of
+    // token tq / 8 in each K256 stage: same arithmetic as mx_quant_kernel, so codes and
+    // scales are the bytes hg_pack would have produced; they go straight to the swizzled activation tile and
+    // to the scale atom in shared memory and never touch HBM.  These warps issue no weight copies, so their
+    // global loads do not queue behind HBM-latency cp.async traffic, and the NEXT stage's 64 bytes are
+    // requested before the current ones are converted.
+    if (p.x) {
+      const int tq = threadIdx.x - 416;
+      const int token = tq >> 3, blk_x = (tq & 7) >> 2, g = tq & 3;
+      const uint16_t* x_row = p.x + int64_t(token) * p.k + g * 32;
+      auto load_x = [&](int kb, int nkb, uint4 (&r)[4]) {
+        if (blk_x < nkb && token < p.tokens) {
+          const uint4* src = reinterpret_cast<const uint4*>(x_row + int64_t(kb + blk_x) * 128);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) r[c] = src[c];
+        } else {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) r[c] = make_uint4(0u, 0u, 0u, 0u);
+        }
+      };
+      uint4 cur[4], nxt[4];
+      int stage = 0;
+      uint32_t phase = 0;
+      int u = unit_begin;
+      WorkUnit wu = first_unit;
+      int kb = wu.kb_begin;
+      pdl_wait();   // x is the previous kernel's output
+      if (u < unit_end) load_x(kb, min(2, wu.kb_end - kb), cur);
+      while (u < unit_end && !error) {
         const int nkb = min(2, wu.kb_end - kb);
+        int next_u = u, next_kb = kb + 2;
+        WorkUnit next_wu = wu;
+        if (next_kb >= wu.kb_end) {
+          ++next_u;
+          if (next_u < unit_end) { next_wu = p.units[next_u]; next_kb = next_wu.kb_begin; }
+        }
+        if (next_u < unit_end) load_x(next_kb, min(2, next_wu.kb_end - next_kb), nxt);
         bool ok = true;
         if (lane == 0) ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag);
         ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;
         if (!ok) { error = kErrLoader; break; }
-        if (!part && blk < nkb) {
-          const uint32_t dst = base + lay.a + uint32_t(stage) * 32768u + dst_off;
-          const uint8_t* src = src0 + int64_t(kb) * 64;
+        if (blk_x < nkb) {
+          const uint32_t row_base = base + lay.b + (uint32_t(stage) * 2u + uint32_t(blk_x)) * lay.b_tile + uint32_t(token) * 128u;
+          const uint32_t sw = uint32_t(token & 7);
+          {
+            float v[32];
+            float amax = 0.f;
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const bool valid = row0 + 8 * i < p.rows[0];
-            cp_async_8(dst + uint32_t(i) * 1024u, valid ? src + int64_t(8 * i) * pitch : p.weight_low, valid ? 8u : 0u);
+            for (int c = 0; c < 4; ++c) {
+              const uint4 raw = cur[c];
+              const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const uint16_t bits = uint16_t(w[i >> 1] >> ((i & 1) * 16));
+                v[c * 8 + i] = p.x_bf16 ? to_float<__nv_bfloat16>(bits) : to_float<__half>(bits);
+                amax = fmaxf(amax, fabsf(v[c * 8 + i]));
+              }
+            }
+            const int e = mx_exponent<false>(amax);
+            const float inv = mx_inverse_scale(e);
+            uint32_t codes[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              codes[i] = cvt_e4m3x2(v[4 * i] * inv, v[4 * i + 1] * inv) | (cvt_e4m3x2(v[4 * i + 2] * inv, v[4 * i + 3] * inv) << 16);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_base + ((uint32_t(2 * g) ^ sw) << 4)),
+                         "r"(codes[0]), "r"(codes[1]), "r"(codes[2]), "r"(codes[3]) : "memory");
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_base + ((uint32_t(2 * g + 1) ^ sw) << 4)),
+                         "r"(codes[4]), "r"(codes[5]), "r"(codes[6]), "r"(codes[7]) : "memory");
+            const uint32_t sf_addr = base + lay.sfb + uint32_t(stage) * 1024u + uint32_t(blk_x) * 512u +
+                                     uint32_t(token & 31) * 16u + uint32_t(token >> 5) * 4u + uint32_t(g);
+            asm volatile("st.shared.u8 [%0], %1;" ::"r"(sf_addr), "r"(uint32_t(e + 127)) : "memory");
           }
         }
-        cp_async_arrive(full_bar(stage));
+        mbar_arrive(full_bar(stage));   // release: the stores above are visible to whoever acquires the barrier
+#pragma unroll
+        for (int c = 0; c < 4; ++c) cur[c] = nxt[c];
         if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+        u = next_u; wu = next_wu; kb = next_kb;
       }
     }
-    // Copies still in flight must land before shared memory is released.
-    asm volatile("cp.async.wait_all;" ::: "memory");
-  } else if (warp == 1 || warp >= 10) {
+  } else if (warp == 1 || (warp >= 10 && warp < 13)) {
     // ------------------------------------------------------------------ MMA issuers (warps 1, 10, 11, 12)
     // A tcgen05 instruction costs its issuing thread on the order of a hundred cycles (descriptor set-up
     // through the uniform datapath) whatever its shape, far more than a 128 x n_tile x 32 MMA occupies the
@@ -811,18 +907,18 @@ struct TcGemm {
   int* d_cut = nullptr;
 };
 
-static void validate(const hg_problem& l, const hg_problem& h) {
+static void validate(const hg_problem& l, const hg_problem& h, bool fused = false) {
   const hg_problem& any = l.rows ? l : h;
   if (l.rows < 0 || h.rows < 0 || l.rows + h.rows == 0) throw std::runtime_error("Hybrid GEMM needs at least one weight row");
   if (any.tokens <= 0 || any.k <= 0 || any.k % 128 || any.outputs <= 0) throw std::runtime_error("Invalid hybrid GEMM shape");
   if (l.rows && h.rows &&
-      (l.tokens != h.tokens || l.k != h.k || l.outputs != h.outputs || l.activation != h.activation ||
-       l.activation_scales != h.activation_scales || l.output != h.output))
+      (l.tokens != h.tokens || l.k != h.k || l.outputs != h.outputs || l.output != h.output ||
+       (!fused && (l.activation != h.activation || l.activation_scales != h.activation_scales))))
     throw std::runtime_error("Low and high partitions must share activation, scales and output");
   auto misaligned = [](const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) != 0; };
   for (const hg_problem* q : {&l, &h}) {
     if (!q->rows) continue;
-    if (!q->weight || !q->activation || !q->weight_scales || !q->activation_scales || !q->ids || !q->output)
+    if (!q->weight || (!fused && (!q->activation || !q->activation_scales)) || !q->weight_scales || !q->ids || !q->output)
       throw std::runtime_error("Null pointer in hybrid GEMM problem");
     if (misaligned(q->weight, 32) || misaligned(q->activation, 16) || misaligned(q->weight_scales, 16) ||
         misaligned(q->activation_scales, 16) || misaligned(q->ids, 4) || misaligned(q->output, 2))
@@ -888,8 +984,14 @@ static void launch_reduce(const Plan& plan, const TcParams& p, const int* cut_ti
   }
 }
 
-void tc_run(TcGemm* g, const hg_problem& l, const hg_problem& h, cudaStream_t stream) {
-  validate(l, h);
+void tc_run(TcGemm* g, const hg_problem& l, const hg_problem& h, cudaStream_t stream, const void* x, int x_dtype) {
+  const bool fused = x != nullptr;
+  validate(l, h, fused);
+  if (fused) {
+    if (g->plan.n_tile != 16) throw std::runtime_error("Fused activation quantisation serves at most 16 tokens");
+    if (x_dtype != HG_DTYPE_F16 && x_dtype != HG_DTYPE_BF16) throw std::runtime_error("Unknown activation dtype");
+    if (reinterpret_cast<uintptr_t>(x) & 15) throw std::runtime_error("Activations must be 16-byte aligned");
+  }
   const hg_problem& any = l.rows ? l : h;
   if (l.rows != g->rows[0] || h.rows != g->rows[1] || any.tokens != g->tokens || any.k != g->k || any.outputs != g->outputs)
     throw std::runtime_error("Hybrid GEMM handle was created for a different shape");
@@ -907,10 +1009,13 @@ void tc_run(TcGemm* g, const hg_problem& l, const hg_problem& h, cudaStream_t st
   p.acc_slots = plan.acc_slots;
   p.external_reduce = plan.external_reduce ? 1 : 0;
   p.weight_low = static_cast<const uint8_t*>(l.weight);
+  p.x = static_cast<const uint16_t*>(x);
+  p.x_bf16 = x_dtype == HG_DTYPE_BF16;
   p.units = g->d_units; p.cta_begin = g->d_cta_begin;
   p.workspace = g->d_workspace; p.counters = g->d_counters; p.status = g->d_status;
-  // An absent high partition still needs a valid descriptor; it is never dereferenced.
-  const CUtensorMap map_act = make_map(any.activation, any.tokens, any.k, plan.n_tile);
+  // An absent high partition (or, in fused mode, the activation map) still needs a valid descriptor; it is
+  // never dereferenced.
+  const CUtensorMap map_act = make_map(fused ? x : any.activation, any.tokens, any.k, plan.n_tile);
   const CUtensorMap map_high = h.rows ? make_map(h.weight, h.rows, h.k, kTileRows) : map_act;
   if (g->dtype == HG_DTYPE_BF16)
     check(launch_kernel(hybrid_gemm_tc_kernel<__nv_bfloat16>, dim3(plan.grid), dim3(kTcThreads), plan.smem_bytes, stream, p, map_high, map_act), "hybrid GEMM launch");

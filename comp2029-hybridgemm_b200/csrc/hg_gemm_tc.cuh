@@ -9,7 +9,7 @@ namespace hg {
 constexpr int kTileRows = 128;  // weight rows per output tile (MMA M)
 constexpr int kTileK = 128;     // K elements per pipeline stage
 constexpr int kMaxStages = 12;
-constexpr int kTcThreads = 416; // warp 0 TMA, 1 and 10-12 MMA issuers, 2-5 epilogue, 6-9 MXFP4 loaders
+constexpr int kTcThreads = 544; // warp 0 TMA, 1 and 10-12 MMA issuers, 2-5 epilogue, 6-9 MXFP4 loaders, 13-16 activation quantisers
 
 // One contiguous run of K128 blocks of one (row tile, token tile).
 struct WorkUnit {
@@ -46,7 +46,10 @@ Plan make_plan(int rows_low, int rows_high, int tokens, int k, int sms, int sche
 
 struct TcGemm;  // opaque device-side state (plan buffers, workspace, counters, status)
 TcGemm* tc_create(const hg_problem& l, const hg_problem& h, int schedule, int dtype, cudaStream_t stream);
-void tc_run(TcGemm*, const hg_problem& l, const hg_problem& h, cudaStream_t stream);
+// `x` (optional): 16-bit activations [tokens,k] to quantise inside the GEMM kernel (at most 16 tokens);
+// the problems' activation / activation_scales pointers are then ignored.
+void tc_run(TcGemm*, const hg_problem& l, const hg_problem& h, cudaStream_t stream, const void* x = nullptr,
+            int x_dtype = HG_DTYPE_BF16);
 void tc_destroy(TcGemm*);
 const Plan& tc_plan(const TcGemm*);
 void tc_kernel_attributes(int* registers, int* local_bytes);

@@ -41,6 +41,13 @@ struct Runner {
     else if (simt_only()) run_simt_pair(l, h, s, 4, dtype);
     else tc_run(tc, l, h, s);
   }
+
+  // Quantise-and-multiply in one launch (decode sizes): see hg_run_x.
+  void run_x(const hg_problem& l, const hg_problem& h, const void* x, int x_dtype, cudaStream_t s) {
+    if (!same_shape(l, low) || !same_shape(h, high)) throw std::runtime_error("Kernel cannot rebind to a different shape");
+    if (!x) throw std::runtime_error("Null activations");
+    tc_run(tc, l, h, s, x, x_dtype);
+  }
 };
 
 static std::string& fused_error() {
@@ -74,6 +81,13 @@ int hg_run(void* handle, const hg_problem* l, const hg_problem* h, void* stream,
   HG_TRY
   if (!handle || !l || !h) throw std::runtime_error("Null argument to hg_run");
   static_cast<hg::Runner*>(handle)->run(*l, *h, static_cast<cudaStream_t>(stream), policy);
+  HG_CATCH
+}
+
+int hg_run_x(void* handle, const hg_problem* l, const hg_problem* h, const void* x, int x_dtype, void* stream) {
+  HG_TRY
+  if (!handle || !l || !h) throw std::runtime_error("Null argument to hg_run_x");
+  static_cast<hg::Runner*>(handle)->run_x(*l, *h, x, x_dtype, static_cast<cudaStream_t>(stream));
   HG_CATCH
 }
 

@@ -28,6 +28,9 @@ class Problem(C.Structure):
 
 
 PACK_MODE = int(os.environ.get("HYGEMM_PACK_MODE", "0"))
+# Decode sizes (at most FUSED_QUANT_TOKENS tokens) quantise the activations inside the GEMM kernel
+# (`hg_run_x`: one launch instead of two, identical bytes); HYGEMM_FUSED_QUANT=0 turns it off.
+FUSED_QUANT_TOKENS = 16 if os.environ.get("HYGEMM_FUSED_QUANT", "1") != "0" else 0
 # Launch policies of hg_run (reference: native.py:14-15).
 POLICIES = {"serial": 0, "concurrent": 1, "high_first": 2, "high_main": 3,
             "gemv_pair1": 4, "gemv_pair2": 5, "gemv_pair4": 6}
@@ -64,6 +67,7 @@ def library():
     lib.hg_create.argtypes = [ci, ci, pp, pp, vp, C.POINTER(vp)]
     lib.hg_create_dtype.argtypes = [ci, ci, pp, pp, vp, ci, C.POINTER(vp)]
     lib.hg_run.argtypes = [vp, pp, pp, vp, ci]
+    lib.hg_run_x.argtypes = [vp, pp, pp, vp, ci, vp]
     lib.hg_info.argtypes = [vp, C.POINTER(ci)]
     lib.hg_status.argtypes = [vp, vp, C.POINTER(ci)]
     lib.hg_destroy.argtypes, lib.hg_destroy.restype = [vp], None
@@ -153,8 +157,32 @@ class DualLinear:
     def __call__(self, x):
         if x.ndim != 2 or x.shape[1] != self.k or x.device != self.w4.device:
             raise ValueError("HyGEMM input shape/device does not match its weights")
+        if 0 < x.shape[0] <= FUSED_QUANT_TOKENS and x.dtype in DTYPES and x.is_contiguous() and not self.plans \
+                and self.low_id != 28:
+            return self._run_fused(x)
         q, sf = pack(x)
         return self.run_packed(q, sf)
+
+    def _run_fused(self, x):
+        """Decode path: activation quantisation inside the GEMM launch (`hg_run_x`)."""
+        tokens = x.shape[0]
+        y = torch.empty((tokens, self.outputs), dtype=self.dtype, device=x.device)
+        low, high, _, low_ref, high_ref = self._rebound(tokens, x, x, y)
+        stream = _stream(x.device)
+        key = (tokens, self.low_id, self.high_id, self.lo.numel(), self.hi.numel())
+        handle = self.handles.get(key)
+        if handle is None:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError(f"HyGEMM shape T={key} must be warmed before graph capture")
+            handle = C.c_void_p()
+            check(library().hg_create_dtype(self.low_id, self.high_id, low_ref, high_ref, stream,
+                                            DTYPES[self.dtype], C.byref(handle)))
+            self.handles[key] = handle
+        status = _lib.hg_run_x(handle, low_ref, high_ref, x.data_ptr(), DTYPES[x.dtype], stream)
+        if status:
+            check(status)
+        self.calls[tokens] = self.calls.get(tokens, 0) + 1
+        return y
 
     def problems(self, q, sf, y):
         """The two `Problem` structs of a call (shared activation, scales and output pointers)."""

@@ -210,3 +210,29 @@ def test_linearity_property_full_size():
     b, _, _ = run_gemm(doubled, torch.bfloat16, 0)
     fa, fb = to_float(a, torch.bfloat16), to_float(b, torch.bfloat16)
     assert np.array_equal(fb, 2 * fa)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_fused_quantisation_launch_equals_pack_then_run(dtype):
+    """`hg_run_x` (decode sizes: activations quantised inside the GEMM launch) must give the bytes of
+    `hg_pack` followed by `hg_run`, for odd K128 counts, both partitions empty or not, and outliers."""
+    torch.manual_seed(11)
+    for outputs, k, high in [(257, 256, 26), (300, 896, 0), (384, 896, 384), (4608, 3584, 512), (3584, 18944, 384)]:
+        w = (torch.randn(outputs, k) * .04).to(dtype).cuda()
+        layer = native.DualLinear(w, torch.randperm(outputs)[:high].cuda())
+        for tokens in (1, 3, 16):
+            x = torch.randn(tokens, k)
+            x[:, ::97] *= 20
+            x[0, :64] = 0
+            x = x.to(dtype).cuda()
+            fused = layer(x)                                   # hg_run_x
+            q, sf = native.pack(x)
+            two_step = layer.run_packed(q, sf)                 # hg_pack + hg_run
+            assert torch.equal(fused.view(torch.int16), two_step.view(torch.int16)), (outputs, k, high, tokens)
+        assert layer.status()[0] == 0
+        layer.close()
+    big = torch.randn(17, 256).to(dtype).cuda()
+    layer = native.DualLinear((torch.randn(257, 256) * .04).to(dtype).cuda(), torch.arange(26).cuda())
+    q, sf = native.pack(big)
+    assert torch.equal(layer(big), layer.run_packed(q, sf))   # 17 tokens: two launches again
+    layer.close()
