@@ -493,11 +493,12 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
         const uint32_t idesc = instr_desc(part == 0, p.n_tile);
         // SFB of token tile t0 sits in column (t0 % 128) / 32 of its 128-token atom.
         const uint32_t sfb_col = uint32_t((wu.token_tile * p.n_tile) % 128) / 32u;
-        // Ownership follows the GLOBAL stage number g (g % issuers == q).  The ring depth is a multiple of
-        // the issuer count, so each ring slot, and with it each full/empty barrier, has exactly one
-        // consumer that sees every round in turn; parity waits stay unambiguous however short units are.
-        const uint32_t first = (uint32_t(q) + uint32_t(p.issuers) - ring % uint32_t(p.issuers)) % uint32_t(p.issuers);
-        for (uint32_t l = first; l < unit_stages && !error; l += uint32_t(p.issuers)) {
+        // Ownership follows the ring SLOT of the global stage number g: issuer (g % stages) % issuers.  Each
+        // ring slot, and with it each full/empty barrier, then has exactly one consumer that sees every round
+        // in turn, so parity waits stay unambiguous however short units are.
+        bool fresh = true;   // this issuer's accumulator has not been written in this unit yet
+        for (uint32_t l = 0; l < unit_stages && !error; ++l) {
+          if (((ring + l) % uint32_t(p.stages)) % uint32_t(p.issuers) != uint32_t(q)) continue;
           const int kb = wu.kb_begin + 2 * int(l);
           const int nkb = min(2, wu.kb_end - kb);
           const uint32_t g = ring + l;
@@ -517,11 +518,12 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
             for (uint32_t j = 0; j < 4; ++j) {
               // 32 K-elements = 32 bytes further along the swizzled row: start address field += 2.
               tc_mma(tmem_d, desc_a + 2 * j, desc_b + 2 * j, idesc | (j << 29) | (j << 4),
-                     (l > first || i > 0 || j > 0) ? 1u : 0u, sf_set, sf_set + 4 + sfb_col);
+                     (!fresh || i > 0 || j > 0) ? 1u : 0u, sf_set, sf_set + 4 + sfb_col);
             }
             ++issued;
           }
           tc_commit(empty_bar(stage));
+          fresh = false;
         }
         ring += unit_stages;
         // Every issuer reports, also one that had no stage in this unit (its accumulator is then skipped).
@@ -552,10 +554,11 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
       if (!epilogue_all(ok)) { error = kErrEpilogue; break; }
       tc_fence_after();
       const int token0 = wu.token_tile * p.n_tile;
-      // Issuers that owned a stage of this unit: global stages ring .. ring + unit_stages - 1, modulo issuers.
+      // Issuers that owned a stage of this unit (global stages ring .. ring + unit_stages - 1, by ring slot).
       const uint32_t unit_stages = uint32_t(wu.kb_end - wu.kb_begin + 1) >> 1;
       uint32_t owners = 0;
-      for (uint32_t l = 0; l < unit_stages && l < uint32_t(p.issuers); ++l) owners |= 1u << ((ring + l) % uint32_t(p.issuers));
+      for (uint32_t l = 0; l < unit_stages && l < uint32_t(p.stages); ++l)
+        owners |= 1u << (((ring + l) % uint32_t(p.stages)) % uint32_t(p.issuers));
       ring += unit_stages;
       const uint32_t taddr = tmem_base + lane_addr + uint32_t(slot) * acc_stride;
       float* ws = wu.nsplit > 1
@@ -700,7 +703,8 @@ Plan make_plan(int rows_low, int rows_high, int tokens, int k, int sms, int sche
   // MMA-issuing threads: two up to n_tile = 64, where TMEM (512 columns) holds two double-buffered
   // accumulators per issuer.  At n_tile = 128 a second issuer would force single-buffered accumulators
   // and a two-stage ring, which measured slower (gate_up M=128: 40.5 vs 34.3 us), so one issuer there.
-  // The pipeline depth is kept a multiple of the issuer count (see the kernel).
+  // The pipeline depth is kept a multiple of the issuer count so the issuers own equally many ring slots
+  // (five stages shared 3:2 measured slower than four shared 2:2).
   plan.issuers = plan.n_tile <= 64 ? 2 : 1;
   if (const char* cap = std::getenv("HYGEMM_TC_ISSUERS"))  // tuning aid: 1, 2 or 4
     plan.issuers = std::max(1, std::min(plan.n_tile <= 32 ? 4 : plan.n_tile <= 64 ? 2 : 2, std::atoi(cap)));
