@@ -49,13 +49,23 @@ namespace hg {
 // Device side
 // ---------------------------------------------------------------------------------------------
 
+// Where the epilogue stores.  Outside tensor-parallel push mode there is one target.  In push mode
+// (hg_run_push) `ptr[w]` is slot `rank` of rank w's receive buffer, `epoch` the device word counting
+// finished exchanges and `parity_stride` the distance in elements between the two halves of a receive buffer.
+struct OutTargets {
+  uint16_t* ptr[HG_TP_MAX_WORLD];
+  int count;
+  const int* epoch;
+  int64_t parity_stride;
+};
+
 struct TcParams {
   int rows[2];
   int tiles[2];
   const uint8_t* sfa[2];
   const int32_t* ids[2];
   const uint8_t* sfb;
-  uint16_t* out;
+  OutTargets out;
   int outputs, tokens, k, kblocks;
   int n_tile, stages, dtype;
   int issuers;    // MMA-issuing threads = independent accumulators per unit (1, 2 or 4)
@@ -197,8 +207,18 @@ __device__ __forceinline__ bool epilogue_all(bool ok) {
 __device__ __forceinline__ void epilogue_sync() { asm volatile("barrier.cta.sync 1, 128;" ::: "memory"); }
 
 template <typename T>
-__device__ __forceinline__ void scatter_store(uint16_t* out, int64_t index, float v) {
-  out[index] = from_float<T>(v);
+__device__ __forceinline__ void scatter_store(const OutTargets& out, int64_t index, float v) {
+  const uint16_t bits = from_float<T>(v);
+  out.ptr[0][index] = bits;
+  for (int w = 1; w < out.count; ++w) out.ptr[w][index] = bits;   // peers' receive buffers (NVLink stores)
+}
+
+// Element offset of the half of the receive buffers this exchange writes (0 outside push mode).  Read
+// after pdl_wait(): the word is advanced by the reduce kernel of the previous exchange.
+__device__ __forceinline__ int64_t out_shift(const OutTargets& out) {
+  if (!out.epoch) return 0;
+  const int e = *reinterpret_cast<const volatile int*>(out.epoch) + 1;
+  return int64_t(e & 1) * out.parity_stride;
 }
 
 // Shared-memory plan.  One pipeline stage covers up to two K128 blocks (K256):
@@ -542,6 +562,7 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
     int acc_it = 0, stored = 0;
     uint32_t ring = 0;
     pdl_wait();  // nothing is written to global memory before every earlier kernel has finished
+    const int64_t shift = out_shift(p.out);
     for (int u = unit_begin; u < unit_end; ++u, ++acc_it) {
       const WorkUnit wu = u == unit_begin ? first_unit : p.units[u];
       const int part = wu.tile >= p.tiles[0];
@@ -584,7 +605,7 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const int token = token0 + c0 + i;
-            if (token < p.tokens) scatter_store<T>(p.out, int64_t(token) * p.outputs + channel, r[i]);
+            if (token < p.tokens) scatter_store<T>(p.out, shift + int64_t(token) * p.outputs + channel, r[i]);
           }
         }
       }
@@ -616,7 +637,7 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
 #pragma unroll
               for (int i = 0; i < 4; ++i)
                 if (token0 + c + i < p.tokens)
-                  scatter_store<T>(p.out, int64_t(token0 + c + i) * p.outputs + channel, sum[i]);
+                  scatter_store<T>(p.out, shift + int64_t(token0 + c + i) * p.outputs + channel, sum[i]);
             }
           }
           if (threadIdx.x == 64) p.counters[wu.counter] = 0;  // ready for the next launch
@@ -651,7 +672,7 @@ struct ReduceParams {
   int rows[2];
   int tiles[2];
   const int32_t* ids[2];
-  uint16_t* out;
+  OutTargets out;
   int outputs, tokens, n_tile;
   const float* workspace;
   const int* cut_tiles;   // 4 ints each: tile, token_tile, ws_slot, nsplit
@@ -670,6 +691,7 @@ splitk_reduce_kernel(const ReduceParams rp) {
   const int row = (part ? tile_v - rp.tiles[0] : tile_v) * kTileRows + int(threadIdx.x);
   if (row >= rp.rows[part]) return;
   const int channel = rp.ids[part][row];
+  const int64_t shift = out_shift(rp.out);
   const int token0 = token_tile * rp.n_tile + c0;
   const float* src = rp.workspace + int64_t(slot) * (int64_t(rp.n_tile) * kTileRows) + int64_t(c0) * kTileRows + threadIdx.x;
   float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -679,7 +701,7 @@ splitk_reduce_kernel(const ReduceParams rp) {
   }
 #pragma unroll
   for (int i = 0; i < 8; ++i)
-    if (token0 + i < rp.tokens) scatter_store<T>(rp.out, int64_t(token0 + i) * rp.outputs + channel, sum[i]);
+    if (token0 + i < rp.tokens) scatter_store<T>(rp.out, shift + int64_t(token0 + i) * rp.outputs + channel, sum[i]);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -988,7 +1010,8 @@ static void launch_reduce(const Plan& plan, const TcParams& p, const int* cut_ti
   }
 }
 
-void tc_run(TcGemm* g, const hg_problem& l, const hg_problem& h, cudaStream_t stream, const void* x, int x_dtype) {
+void tc_run(TcGemm* g, const hg_problem& l, const hg_problem& h, cudaStream_t stream, const void* x, int x_dtype,
+            const PeerPush* push) {
   const bool fused = x != nullptr;
   validate(l, h, fused);
   if (fused) {
@@ -1006,7 +1029,24 @@ void tc_run(TcGemm* g, const hg_problem& l, const hg_problem& h, cudaStream_t st
   p.sfa[0] = static_cast<const uint8_t*>(l.weight_scales); p.sfa[1] = static_cast<const uint8_t*>(h.weight_scales);
   p.ids[0] = static_cast<const int32_t*>(l.ids); p.ids[1] = static_cast<const int32_t*>(h.ids);
   p.sfb = static_cast<const uint8_t*>(any.activation_scales);
-  p.out = static_cast<uint16_t*>(any.output);
+  if (push) {
+    // Slot `rank` of every rank's receive buffer; the own buffer first so a one-rank world behaves like hg_run.
+    if (push->world < 1 || push->world > HG_TP_MAX_WORLD || push->rank < 0 || push->rank >= push->world)
+      throw std::runtime_error("Tensor-parallel world must be 1..8 with rank inside it");
+    if (!push->recv || !push->state) throw std::runtime_error("Null receive buffers or state");
+    if (push->slot_elems < int64_t(any.tokens) * any.outputs) throw std::runtime_error("Receive slot smaller than tokens x outputs");
+    for (int i = 0; i < push->world; ++i) {
+      const int w = (push->rank + i) % push->world;
+      if (!push->recv[w] || (reinterpret_cast<uintptr_t>(push->recv[w]) & 15)) throw std::runtime_error("Receive buffers must be 16-byte aligned");
+      p.out.ptr[i] = static_cast<uint16_t*>(push->recv[w]) + int64_t(push->rank) * push->slot_elems;
+    }
+    p.out.count = push->world;
+    p.out.epoch = push->state;
+    p.out.parity_stride = int64_t(push->world) * push->slot_elems;
+  } else {
+    p.out.ptr[0] = static_cast<uint16_t*>(any.output);
+    p.out.count = 1;
+  }
   p.outputs = any.outputs; p.tokens = any.tokens; p.k = any.k; p.kblocks = any.k / kTileK;
   p.n_tile = plan.n_tile; p.stages = plan.stages; p.dtype = g->dtype; p.tmem_cols = uint32_t(plan.tmem_cols);
   p.issuers = plan.issuers;
@@ -1149,7 +1189,8 @@ void tc_run_static(int schedule, const hg_problem& l, const hg_problem& h, int d
   p.sfa[0] = static_cast<const uint8_t*>(l.weight_scales); p.sfa[1] = static_cast<const uint8_t*>(h.weight_scales);
   p.ids[0] = static_cast<const int32_t*>(l.ids); p.ids[1] = static_cast<const int32_t*>(h.ids);
   p.sfb = static_cast<const uint8_t*>(any.activation_scales);
-  p.out = static_cast<uint16_t*>(any.output);
+  p.out.ptr[0] = static_cast<uint16_t*>(any.output);
+  p.out.count = 1;
   p.outputs = any.outputs; p.tokens = any.tokens; p.k = any.k; p.kblocks = any.k / kTileK;
   p.n_tile = plan.n_tile; p.stages = plan.stages; p.dtype = dtype; p.tmem_cols = uint32_t(plan.tmem_cols);
   p.issuers = plan.issuers;

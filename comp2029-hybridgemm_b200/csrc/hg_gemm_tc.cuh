@@ -48,8 +48,16 @@ struct TcGemm;  // opaque device-side state (plan buffers, workspace, counters, 
 TcGemm* tc_create(const hg_problem& l, const hg_problem& h, int schedule, int dtype, cudaStream_t stream);
 // `x` (optional): 16-bit activations [tokens,k] to quantise inside the GEMM kernel (at most 16 tokens);
 // the problems' activation / activation_scales pointers are then ignored.
+// `push` (optional): row-parallel tensor parallelism; the epilogue stores the partial result into slot
+// `rank` of every rank's receive buffer (see hg_run_push) instead of the problems' `output`.
+struct PeerPush {
+  void* const* recv;   // world base pointers, as mapped on this GPU
+  int world, rank;
+  int64_t slot_elems;  // 16-bit elements per rank slot
+  const int* state;    // device word counting finished exchanges
+};
 void tc_run(TcGemm*, const hg_problem& l, const hg_problem& h, cudaStream_t stream, const void* x = nullptr,
-            int x_dtype = HG_DTYPE_BF16);
+            int x_dtype = HG_DTYPE_BF16, const PeerPush* push = nullptr);
 void tc_destroy(TcGemm*);
 const Plan& tc_plan(const TcGemm*);
 void tc_kernel_attributes(int* registers, int* local_bytes);

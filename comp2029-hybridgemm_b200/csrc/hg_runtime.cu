@@ -48,6 +48,12 @@ struct Runner {
     if (!x) throw std::runtime_error("Null activations");
     tc_run(tc, l, h, s, x, x_dtype);
   }
+
+  // Row-parallel tensor parallelism: partial results go to every rank's receive buffer (see hg_run_push).
+  void run_push(const hg_problem& l, const hg_problem& h, const void* x, int x_dtype, const PeerPush& push, cudaStream_t s) {
+    if (!same_shape(l, low) || !same_shape(h, high)) throw std::runtime_error("Kernel cannot rebind to a different shape");
+    tc_run(tc, l, h, s, x, x_dtype, &push);
+  }
 };
 
 static std::string& fused_error() {
@@ -88,6 +94,15 @@ int hg_run_x(void* handle, const hg_problem* l, const hg_problem* h, const void*
   HG_TRY
   if (!handle || !l || !h) throw std::runtime_error("Null argument to hg_run_x");
   static_cast<hg::Runner*>(handle)->run_x(*l, *h, x, x_dtype, static_cast<cudaStream_t>(stream));
+  HG_CATCH
+}
+
+int hg_run_push(void* handle, const hg_problem* l, const hg_problem* h, const void* x, int x_dtype,
+                void* const* recv, int world, int rank, int64_t slot_elems, const int* state, void* stream) {
+  HG_TRY
+  if (!handle || !l || !h) throw std::runtime_error("Null argument to hg_run_push");
+  const hg::PeerPush push{recv, world, rank, slot_elems, state};
+  static_cast<hg::Runner*>(handle)->run_push(*l, *h, x, x_dtype, push, static_cast<cudaStream_t>(stream));
   HG_CATCH
 }
 

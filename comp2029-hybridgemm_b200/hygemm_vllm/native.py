@@ -31,6 +31,10 @@ PACK_MODE = int(os.environ.get("HYGEMM_PACK_MODE", "0"))
 # Decode sizes (at most FUSED_QUANT_TOKENS tokens) quantise the activations inside the GEMM kernel
 # (`hg_run_x`: one launch instead of two, identical bytes); HYGEMM_FUSED_QUANT=0 turns it off.
 FUSED_QUANT_TOKENS = 16 if os.environ.get("HYGEMM_FUSED_QUANT", "1") != "0" else 0
+# Every CTA quantises the K slice it multiplies, so the work repeats once per row tile; layers wider than this
+# many output channels keep the separate quantiser launch (gate_up, 37888 wide, measured 30.8 us with its own
+# quantiser launch against 36.3 us fused at 16 tokens; the narrow layers gain from the missing launch).
+FUSED_QUANT_MAX_OUTPUTS = int(os.environ.get("HYGEMM_FUSED_QUANT_MAX_OUTPUTS", "8192"))
 # Launch policies of hg_run (reference: native.py:14-15).
 POLICIES = {"serial": 0, "concurrent": 1, "high_first": 2, "high_main": 3,
             "gemv_pair1": 4, "gemv_pair2": 5, "gemv_pair4": 6}
@@ -73,6 +77,9 @@ def library():
     lib.hg_destroy.argtypes, lib.hg_destroy.restype = [vp], None
     lib.hg_plan.argtypes = [ci] * 6 + [C.POINTER(ci), C.POINTER(ci), ci]
     lib.hg_run_static.argtypes = [ci, pp, pp, vp, ci]
+    lib.hg_run_push.argtypes = [vp, pp, pp, vp, ci, C.POINTER(vp), ci, ci, C.c_int64, vp, vp]
+    lib.hg_tp_reduce.argtypes = [vp, vp, C.c_int64, C.c_int64, ci, ci, C.POINTER(vp), vp, ci, vp]
+    lib.hg_tp_status.argtypes = [vp, vp, C.POINTER(ci)]
     lib.hg_fused_error.restype = C.c_char_p
     lib.hg_fused_create.argtypes = [ci, pp, pp, vp, C.POINTER(vp)]
     lib.hg_fused_create_dtype.argtypes = [ci, pp, pp, vp, ci, C.POINTER(vp)]
@@ -158,7 +165,7 @@ class DualLinear:
         if x.ndim != 2 or x.shape[1] != self.k or x.device != self.w4.device:
             raise ValueError("HyGEMM input shape/device does not match its weights")
         if 0 < x.shape[0] <= FUSED_QUANT_TOKENS and x.dtype in DTYPES and x.is_contiguous() and not self.plans \
-                and self.low_id != 28:
+                and self.low_id != 28 and self.outputs <= FUSED_QUANT_MAX_OUTPUTS:
             return self._run_fused(x)
         q, sf = pack(x)
         return self.run_packed(q, sf)
@@ -238,6 +245,46 @@ class DualLinear:
         status = _lib.hg_run(handle, low_ref, high_ref, stream, policy)
         if status:
             check(status)
+        self.calls[tokens] = self.calls.get(tokens, 0) + 1
+        return y
+
+    def run_exchange(self, exchange, x=None, q=None, sf=None):
+        """Row-parallel shard: the GEMM pushes its partial sums into every rank's receive buffer from its
+        epilogue and a second launch waits for all ranks and adds them (`hg_run_push` + `hg_tp_reduce`).
+
+        `exchange` is a `tp.PeerExchange`.  Pass 16-bit `x` (at most FUSED_QUANT_TOKENS tokens, quantised in
+        the GEMM launch) or prepacked `(q, sf)`.  Returns the summed `[tokens, outputs]`, identical on every rank.
+        """
+        fused = x is not None
+        src = x if fused else q
+        tokens = src.shape[0]
+        if src.ndim != 2 or src.shape[1] != self.k or not src.is_contiguous() or tokens == 0:
+            raise ValueError("HyGEMM input shape does not match its weights")
+        if fused and not (tokens <= FUSED_QUANT_TOKENS and x.dtype in DTYPES):
+            raise ValueError("Fused quantisation serves at most 16 tokens of FP16/BF16")
+        if not fused and (sf is None or sf.numel() != scale_size(tokens, self.k)):
+            raise ValueError("Invalid prepacked MXFP8 scale buffer")
+        if tokens * self.outputs > exchange.slot_elems or self.dtype != exchange.dtype:
+            raise ValueError("Exchange buffers are too small or of another dtype")
+        y = torch.empty((tokens, self.outputs), dtype=self.dtype, device=src.device)
+        low, high, _, low_ref, high_ref = self._rebound(tokens, src, src if fused else sf, y)
+        stream = _stream(src.device)
+        key = (tokens, self.low_id, self.high_id, self.lo.numel(), self.hi.numel())
+        handle = self.handles.get(key)
+        if handle is None:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError(f"HyGEMM shape T={key} must be warmed before graph capture")
+            handle = C.c_void_p()
+            check(library().hg_create_dtype(self.low_id, self.high_id, low_ref, high_ref, stream,
+                                            DTYPES[self.dtype], C.byref(handle)))
+            self.handles[key] = handle
+        lib = library()
+        check(lib.hg_run_push(handle, low_ref, high_ref, x.data_ptr() if fused else None,
+                              DTYPES[x.dtype] if fused else 0, exchange.recv_ptrs, exchange.world, exchange.rank,
+                              exchange.slot_elems, exchange.state.data_ptr(), stream))
+        check(lib.hg_tp_reduce(exchange.recv.data_ptr(), y.data_ptr(), tokens * self.outputs, exchange.slot_elems,
+                               exchange.world, exchange.rank, exchange.flag_ptrs, exchange.state.data_ptr(),
+                               DTYPES[self.dtype], stream))
         self.calls[tokens] = self.calls.get(tokens, 0) + 1
         return y
 

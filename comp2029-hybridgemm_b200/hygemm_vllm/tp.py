@@ -87,3 +87,48 @@ def all_reduce_partial(y: torch.Tensor, group: dist.ProcessGroup | None = None) 
     if dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_reduce(y, group=group)
     return y
+
+
+class PeerExchange:
+    """Buffers of the fused row-parallel GEMM + exchange (`DualLinear.run_exchange`).
+
+    Every rank allocates, in memory mapped on all peers (torch symmetric memory over CUDA IPC), a receive
+    buffer of 2 x world x slot_elems elements and a flag array; the GEMM epilogue of rank r stores its
+    partial result into slot r of every rank's buffer over NVLink, and the reduce launch waits on the flags
+    and sums the slots in rank order.  One instance serves every row-parallel layer of a model whose
+    `tokens x outputs` fits `max_elems`, as the exchanges of a stream are ordered.  NVLink multicast is
+    not used (plain peer stores), so the buffers are never bound to a multicast object by this class.
+    """
+
+    def __init__(self, group: dist.ProcessGroup, max_elems: int, dtype: torch.dtype, device: torch.device):
+        import ctypes as C
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("PeerExchange serves at most 8 ranks of one NVLink domain")
+        self.dtype, self.group = dtype, group
+        self.slot_elems = -(-max_elems // 8) * 8
+        self.recv = symm.empty(2 * self.world * self.slot_elems, dtype=dtype, device=device)
+        self.flags = symm.empty(64, dtype=torch.int32, device=device)
+        self.recv.zero_()
+        self.flags.zero_()
+        self.state = torch.zeros(4, dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        self._handles = (symm.rendezvous(self.recv, group), symm.rendezvous(self.flags, group))
+        self.recv_ptrs = (C.c_void_p * self.world)(*[int(p) for p in self._handles[0].buffer_ptrs])
+        self.flag_ptrs = (C.c_void_p * self.world)(*[int(p) for p in self._handles[1].buffer_ptrs])
+        if self.recv_ptrs[self.rank] != self.recv.data_ptr():
+            raise RuntimeError("symmetric memory did not return this rank's own buffer at its rank index")
+        dist.barrier(group)
+        torch.cuda.synchronize(device)
+
+    def status(self) -> int:
+        """0, or 1000 + the rank whose partials never arrived within the wait limit (cleared by the read)."""
+        import ctypes as C
+        from . import native
+        out = C.c_int(0)
+        native.check(native.library().hg_tp_status(self.state.data_ptr(), torch.cuda.current_stream().cuda_stream,
+                                                   C.byref(out)))
+        return out.value

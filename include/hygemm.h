@@ -137,6 +137,34 @@ int hg_plan(int rows_low, int rows_high, int tokens, int k, int sms, int schedul
  *     sizes; nothing is launched.  Use hg_create/hg_run for such shapes. */
 int hg_run_static(int schedule, const hg_problem* low, const hg_problem* high, void* stream, int dtype);
 
+/* ---- Row-parallel tensor parallelism: GEMM fused with the exchange of its partial sums over peer memory.
+ * No counterpart in the reference, which refuses tensor_parallel_size > 1
+ * (integrations/vllm/hygemm_vllm/quantization.py:81-83).
+ *
+ * Every rank owns a receive buffer of 2 x world x slot_elems 16-bit elements and a flag array of `world`
+ * ints, both mapped on every peer (CUDA IPC / symmetric memory), plus three private ints of `state`
+ * (exchange count, block ticket, status), all zeroed once.  One exchange is two calls on every rank:
+ *
+ *   hg_run_push    the GEMM of hg_run (or hg_run_x when `x` is not null), whose epilogue stores this rank's
+ *                  partial [tokens,outputs] into slot `rank` of EVERY rank's receive buffer (`recv[w]` =
+ *                  base of rank w's buffer as mapped here; recv[rank] is the own one) tile by tile, so the
+ *                  NVLink transfer overlaps the main loop.  `output` of the problems is ignored.
+ *   hg_tp_reduce   publishes "my partials are written" to every peer's flag array, waits (bounded: about
+ *                  one second, then status = 1000 + rank waited for, readable with hg_tp_status) for all
+ *                  world flags in the own array, and sums the world slots in rank order into `out`
+ *                  (identical bits on every rank).  It then advances `state[0]`.
+ *
+ * The two halves of the receive buffer are used alternately (by the parity of state[0] + 1), which is
+ * what makes the next exchange safe to start while a slow peer still sums the previous one.  Both calls
+ * allocate nothing and are graph-capturable: the exchange count lives in device memory.  world <= 8. */
+#define HG_TP_MAX_WORLD 8
+int hg_run_push(void* handle, const hg_problem* low, const hg_problem* high, const void* x, int x_dtype,
+                void* const* recv, int world, int rank, int64_t slot_elems, const int* state, void* stream);
+int hg_tp_reduce(const void* recv_own, void* out, int64_t elems, int64_t slot_elems, int world, int rank,
+                 int* const* flags, int* state, int dtype, void* stream);
+/* Reads and clears state[2] (0 = every wait was satisfied). */
+int hg_tp_status(int* state, void* stream, int* status);
+
 /* Single-kernel path kept for binding compatibility
  * (integrations/vllm/native/fused_probe.cu:7-28).  The tcgen05 kernel already
  * covers both partitions in one launch, so these wrap the same implementation

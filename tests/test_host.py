@@ -197,3 +197,14 @@ def test_row_parallel_shards_and_l2norm_rule():
     ids = tp.select_by_l2norm(w, 0.1, 128)
     assert len(ids) == 128 and {5, 17, 900} <= set(ids) and ids == sorted(ids)
     assert tp.select_by_l2norm(w, 0.0) == []
+
+
+def test_exchange_arguments_are_checked():
+    """hg_run_push / hg_tp_reduce refuse bad arguments before touching a device."""
+    lib = native.library()
+    flags = (C.c_void_p * 2)(16, 16)
+    assert lib.hg_tp_reduce(None, None, 8, 8, 2, 0, flags, None, 1, None) == -1
+    assert lib.hg_tp_reduce(16, 16, 12, 16, 2, 0, flags, 16, 1, None) == -1
+    assert b"multiples of 8" in lib.hg_last_error()
+    assert lib.hg_tp_reduce(16, 16, 8, 8, 9, 0, flags, 16, 1, None) == -1
+    assert lib.hg_run_push(None, None, None, None, 0, None, 2, 0, 8, None, None) == -1
