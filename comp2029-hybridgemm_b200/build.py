@@ -8,7 +8,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIBRARY = HERE / "lib" / "libhygemm_b200.so"
-SOURCES = ["hg_quant.cu", "hg_gemm_simt.cu", "hg_gemm_tc.cu", "hg_runtime.cu", "hg_tp.cu"]
+SOURCES = ["hg_quant.cu", "hg_gemm_simt.cu", "hg_gemm_tc.cu", "hg_runtime.cu", "hg_tp.cu", "hg_clip.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "-shared", "-cudart", "static"]
 

@@ -165,6 +165,16 @@ int hg_tp_reduce(const void* recv_own, void* out, int64_t elems, int64_t slot_el
 /* Reads and clears state[2] (0 = every wait was satisfied). */
 int hg_tp_status(int* state, void* stream, int* status);
 
+/* Offline MXFP4 quantiser with an exponent search (integrations/vllm/allocation/fp4_quant.py:28-58,
+ * `quantize`; there a chain of torch ops, here one kernel).  `in` is [rows,k] 16-bit (HG_DTYPE_*), `importance`
+ * null or k non-negative floats weighting the squared error per input channel.  Per K32 group the
+ * round-to-nearest codes and scale of hg_pack(fp4) are the baseline; each non-zero entry of `offsets` (at most
+ * 8, in order) moves the scale byte, clamped to [0,254], re-rounds the group (saturating) and wins if its
+ * weighted squared error is strictly smaller.  Writes packed codes [rows,k/2] (even k in the low nibble) and
+ * LOGICAL scale bytes [rows,k/32] (offline_weights.physical_scales lays them out in atoms). */
+int hg_clip_pack(const void* in, const float* importance, void* q4, void* scales, int rows, int k,
+                 const int* offsets, int n_offsets, int dtype, void* stream);
+
 /* Single-kernel path kept for binding compatibility
  * (integrations/vllm/native/fused_probe.cu:7-28).  The tcgen05 kernel already
  * covers both partitions in one launch, so these wrap the same implementation

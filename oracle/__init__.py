@@ -42,6 +42,7 @@ def lib():
         L.hgo_pack.argtypes = [u16p, u8p, u8p, C.c_int, C.c_int, C.c_int, C.c_int]
         L.hgo_silu_pack.argtypes = [u16p, u8p, u8p, u16p, C.c_int, C.c_int, C.c_int]
         L.hgo_decode.argtypes = [u8p, u8p, f32p, C.c_int, C.c_int, C.c_int]
+        L.hgo_clip_pack.argtypes = [u16p, f32p, u8p, u8p, C.c_int, C.c_int, i32p, C.c_int, C.c_int]
         L.hgo_hybrid_linear.argtypes = [u8p, u8p, i32p, C.c_int, u8p, u8p, i32p, C.c_int,
                                         u8p, u8p, C.c_int, C.c_int, C.c_int, u16p, C.c_int, f32p]
         L.hgo_exact_weights.argtypes = [i32p, C.c_int, C.c_int, C.c_int, u8p, u8p]
@@ -120,6 +121,23 @@ def silu_pack(x, bf16: bool = True, debug: bool = False):
     if status:
         raise ValueError("Invalid SwiGLU pack arguments")
     return (q, sf, dbg) if debug else (q, sf)
+
+
+def clip_pack(x, importance=None, offsets=(0, -1, -2), bf16: bool = True):
+    """Offline MXFP4 exponent search → (packed codes ``[rows,k/2]``, logical scale bytes ``[rows,k/32]``)."""
+    bits = as_u16(x)
+    rows, k = bits.shape
+    q4 = np.zeros((rows, k // 2), dtype=np.uint8)
+    scales = np.zeros((rows, k // 32), dtype=np.uint8)
+    weight = None if importance is None else np.ascontiguousarray(importance, dtype=np.float32)
+    if weight is not None and weight.shape != (k,):
+        raise ValueError("importance must have k entries")
+    shifts = np.ascontiguousarray(offsets, dtype=np.int32)
+    status = lib().hgo_clip_pack(_ptr(bits, C.c_uint16), _ptr(weight, C.c_float), _ptr(q4, C.c_uint8),
+                                 _ptr(scales, C.c_uint8), rows, k, _ptr(shifts, C.c_int32), len(shifts), int(bf16))
+    if status:
+        raise ValueError("Invalid clipping-quantiser arguments")
+    return q4, scales
 
 
 def decode(q: np.ndarray, sf: np.ndarray, k: int, fp4: bool) -> np.ndarray:

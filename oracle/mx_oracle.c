@@ -304,6 +304,79 @@ int hgo_silu_pack(const uint16_t* in, uint8_t* q, uint8_t* sf, uint16_t* debug, 
 }
 
 /* ------------------------------------------------------------------------- */
+/* Offline MXFP4 exponent search: integrations/vllm/allocation/fp4_quant.py   */
+/* :28-58 (quantize).  Per K32 group the round-to-nearest result of hgo_pack  */
+/* is the baseline; for every non-zero offset in the given order the scale    */
+/* byte is moved by that offset (clamped to [0,254]), the group re-rounded    */
+/* with codes_rne and kept if its importance-weighted squared error is        */
+/* STRICTLY smaller than the best so far.  Output: packed codes [rows,k/2]    */
+/* and logical scale bytes [rows,k/32].                                       */
+/*                                                                            */
+/* The reference sums the 32 error terms with a torch reduction whose order   */
+/* is not specified; here the order is fixed: four runs of eight terms added  */
+/* left to right, then (r0+r1)+(r2+r3).  The two can differ only where two    */
+/* candidates tie to within fp32 rounding of the sum.                         */
+/* ------------------------------------------------------------------------- */
+
+typedef struct {
+  const uint16_t* in; const float* importance; uint8_t* q4; uint8_t* scales;
+  int k, bf16, n_offsets; const int* offsets;
+} clip_ctx;
+
+static float group_error(const float* v, const uint8_t* code, float scale, const float* weight) {
+  float run[4];
+  for (int j = 0; j < 4; ++j) {
+    float sum = 0.f;
+    for (int i = 0; i < 8; ++i) {
+      float diff = kE2M1[code[8 * j + i]] * scale - v[8 * j + i];
+      float term = diff * diff;
+      term = term * (weight ? weight[8 * j + i] : 1.f);
+      sum = sum + term;
+    }
+    run[j] = sum;
+  }
+  return (run[0] + run[1]) + (run[2] + run[3]);
+}
+
+static void clip_rows(int begin, int end, void* p) {
+  clip_ctx* c = (clip_ctx*)p;
+  const int k = c->k, groups = k / 32;
+  for (int r = begin; r < end; ++r)
+    for (int g = 0; g < groups; ++g) {
+      float v[32], amax = 0.f;
+      for (int i = 0; i < 32; ++i) {
+        v[i] = load16(c->in, (int64_t)r * k + g * 32 + i, c->bf16);
+        amax = fmaxf(amax, fabsf(v[i]));
+      }
+      const float* weight = c->importance ? c->importance + g * 32 : NULL;
+      const int base = hgo_exponent_literal(amax, 1) + 127;
+      uint8_t best_code[32], code[32];
+      int best_byte = base;
+      for (int i = 0; i < 32; ++i) best_code[i] = hgo_e2m1_from_float(ldexpf(v[i], -(base - 127)));
+      float best = group_error(v, best_code, ldexpf(1.f, base - 127), weight);
+      for (int o = 0; o < c->n_offsets; ++o) {
+        if (c->offsets[o] == 0) continue;
+        int byte = base + c->offsets[o];
+        byte = byte < 0 ? 0 : (byte > 254 ? 254 : byte);
+        for (int i = 0; i < 32; ++i) code[i] = hgo_e2m1_from_float(ldexpf(v[i], -(byte - 127)));
+        float err = group_error(v, code, ldexpf(1.f, byte - 127), weight);
+        if (err < best) { best = err; best_byte = byte; memcpy(best_code, code, 32); }
+      }
+      c->scales[(int64_t)r * groups + g] = (uint8_t)best_byte;
+      for (int i = 0; i < 32; i += 2)
+        c->q4[((int64_t)r * k + g * 32 + i) / 2] = (uint8_t)(best_code[i] | (best_code[i + 1] << 4));
+    }
+}
+
+int hgo_clip_pack(const uint16_t* in, const float* importance, uint8_t* q4, uint8_t* scales, int rows, int k,
+                  const int* offsets, int n_offsets, int bf16) {
+  if (rows <= 0 || k <= 0 || k % 128 || !in || !q4 || !scales || n_offsets < 0 || (n_offsets && !offsets)) return -1;
+  clip_ctx ctx = {in, importance, q4, scales, k, bf16, n_offsets, offsets};
+  parallel_rows(rows, clip_rows, &ctx);
+  return 0;
+}
+
+/* ------------------------------------------------------------------------- */
 /* Dequantise: integrations/vllm/test_components.py:10-24 (decode_mx)         */
 /* ------------------------------------------------------------------------- */
 

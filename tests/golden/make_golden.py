@@ -21,6 +21,16 @@ Sources of truth, by fixture:
   CUDA quantiser calls) for every fp16 and bf16 bit pattern, produced by
   ``cutlass_codecs.cpp`` against the CUTLASS headers found in the container.
 
+* ``clip_search.npz`` — the exponent search of
+  ``integrations/vllm/allocation/fp4_quant.py:28-58`` (``quantize``).  That
+  function itself asserts a CUDA tensor and calls the CUDA ``pack``, so it cannot
+  run here; the fixture composes the reference's own CPU-runnable pieces
+  (``unpack``, ``codes_rne``, ``pack_codes``, ``decode_logical``,
+  ``offline_weights.logical_scales``) in the order ``quantize`` uses them, with
+  the round-to-nearest baseline taken from this repository's oracle (whose
+  quantiser is pinned by the codec fixtures).  Error sums are torch CPU
+  reductions.
+
 The quantised operands fed to ``reference_linear`` come from the CPU oracle of
 this repository; the fixture pins the *decode and matmul* half against the
 reference, the quantiser half is pinned by the codec fixtures.
@@ -121,6 +131,42 @@ def main():
                                 y_half=oracle.as_u16(y.half()), y_bf16=oracle.as_u16(y.bfloat16())).items():
             lin[f"{tag}__{name}"] = value
     np.savez_compressed(HERE / "reference_linear.npz", **lin)
+
+    # ---- offline exponent search (fp4_quant.quantize, composed from its CPU-runnable pieces) -----------
+    clip = {}
+    torch.manual_seed(20261024 + 7)
+    for tag, rows, k, weighted, offsets in [("plain", 64, 256, False, (0, -1, -2)), ("weighted", 48, 384, True, (0, -1, -2)),
+                                            ("up", 32, 128, False, (0, 1, -1)), ("heavy", 32, 256, True, (0, -1, -2, -3))]:
+        w = (torch.randn(rows, k) * .05)
+        w[torch.rand(rows, k) < .02] *= 12          # outliers, so that clipping sometimes wins
+        w[0, :32] = 0                               # an all-zero group
+        w = w.half()
+        importance = (torch.rand(k) * 4).float() if weighted else None
+        q, sf = oracle.pack(w, fp4=True, bf16=False)
+        q, sf = torch.from_numpy(q), torch.from_numpy(sf)
+        logical = ow.logical_scales(sf, rows, k)
+        source = w.float().reshape(rows, k // 32, 32)
+        weight = (torch.ones(k) if importance is None else importance).reshape(1, k // 32, 32)
+        best_error = ((fp4_quant.decode_logical(q, logical, k).reshape_as(source) - source).square() * weight).sum(-1)
+        best_codes, best_scale = fp4_quant.unpack(q).reshape(rows, k // 32, 32), logical.clone()
+        for shift in offsets:
+            if shift == 0:
+                continue
+            exponent = (logical.to(torch.int16) + shift).clamp(0, 254).to(torch.uint8)
+            codes = fp4_quant.codes_rne(source / torch.exp2(exponent.float() - 127)[:, :, None])
+            values = fp4_quant.decode_logical(fp4_quant.pack_codes(codes.reshape(rows, k)), exponent, k).reshape_as(source)
+            error = ((values - source).square() * weight).sum(-1)
+            better = error < best_error
+            best_error = torch.where(better, error, best_error)
+            best_codes = torch.where(better[:, :, None], codes, best_codes)
+            best_scale = torch.where(better, exponent, best_scale)
+        clip[tag + "__w"] = oracle.as_u16(w)
+        clip[tag + "__importance"] = np.zeros(0, np.float32) if importance is None else importance.numpy()
+        clip[tag + "__offsets"] = np.array(offsets, dtype=np.int32)
+        clip[tag + "__q4"] = fp4_quant.pack_codes(best_codes.reshape(rows, k)).numpy()
+        clip[tag + "__scales"] = best_scale.numpy()
+        clip[tag + "__error"] = best_error.numpy().astype(np.float32)
+    np.savez_compressed(HERE / "clip_search.npz", **clip)
 
     # ---- CUTLASS element conversions -----------------------------------------------------
     with tempfile.TemporaryDirectory() as tmp:

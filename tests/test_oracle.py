@@ -203,3 +203,45 @@ def test_silu_pack_equals_two_step_restatement():
         assert (got.view(torch.int16) != v.view(torch.int16)).float().mean() < 1e-3   # expf implementations differ by <=1ulp
         q2, sf2 = oracle.pack(got, fp4=False, bf16=bf16)
         assert np.array_equal(q, q2) and np.array_equal(sf, sf2)
+
+
+# ---- offline exponent search (allocation/fp4_quant.py:28-58) -------------------------------------------------
+
+@pytest.mark.parametrize("tag", ["plain", "weighted", "up", "heavy"])
+def test_clip_search_matches_reference_composition(golden, tag):
+    """Codes and scale bytes equal the reference's pieces composed as its `quantize` composes them."""
+    CLIP = golden("clip_search.npz")
+    bits, importance = CLIP[tag + "__w"], CLIP[tag + "__importance"]
+    offsets = tuple(int(o) for o in CLIP[tag + "__offsets"])
+    q4, scales = oracle.clip_pack(bits, importance if importance.size else None, offsets, bf16=False)
+    assert (scales == CLIP[tag + "__scales"]).all() and (q4 == CLIP[tag + "__q4"]).all()
+    base_q, base_sf = oracle.pack(bits, fp4=True, bf16=False)
+    base = base_sf[oracle.scale_indices(*bits.shape)]
+    assert (scales != base).any()                                   # the fixture exercises the search
+    assert ((scales.astype(int) - base.astype(int)) != 0).sum() == (scales != base).sum()
+
+
+def test_clip_search_without_offsets_is_pack():
+    rng = np.random.default_rng(5)
+    w = (rng.standard_normal((40, 256)) * 0.1).astype(np.float16)
+    q4, scales = oracle.clip_pack(w.view(np.uint16), None, (), bf16=False)
+    base_q, base_sf = oracle.pack(w.view(np.uint16), fp4=True, bf16=False)
+    assert (q4 == base_q).all() and (scales == base_sf[oracle.scale_indices(40, 256)]).all()
+
+
+def test_clip_search_never_increases_the_weighted_error():
+    rng = np.random.default_rng(6)
+    w = (rng.standard_normal((64, 384)) * 0.05).astype(np.float16)
+    w[rng.random((64, 384)) < 0.03] *= 10
+    importance = rng.random(384).astype(np.float32) * 2
+    q4, scales = oracle.clip_pack(w.view(np.uint16), importance, (0, -1, -2), bf16=False)
+    base_q, base_sf = oracle.pack(w.view(np.uint16), fp4=True, bf16=False)
+
+    def error(q, logical):
+        sf = np.full(oracle.scale_size(64, 384), 127, np.uint8)
+        sf[oracle.scale_indices(64, 384)] = logical
+        diff = oracle.decode(q, sf, 384, True).astype(np.float64) - w.astype(np.float64)
+        return ((diff ** 2) * importance).reshape(64, 12, 32).sum(-1)
+
+    after, before = error(q4, scales), error(base_q, base_sf[oracle.scale_indices(64, 384)])
+    assert (after <= before * (1 + 1e-6) + 1e-25).all() and after.sum() < before.sum()
