@@ -59,6 +59,16 @@ struct OutTargets {
   int64_t parity_stride;
 };
 
+// Per-CTA start of the schedule, passed BY VALUE as a kernel parameter: a CTA learns its first work unit
+// from the constant bank instead of from two dependent global loads (about a microsecond before the first
+// weight request can leave).  Grids larger than kMaxHeads fall back to the arrays in global memory.
+constexpr int kMaxHeads = 160;
+struct CtaHeads {
+  int valid;                   // 0: read cta_begin / units from global memory
+  int begin[kMaxHeads + 1];
+  WorkUnit first[kMaxHeads];
+};
+
 struct TcParams {
   int rows[2];
   int tiles[2];
@@ -72,6 +82,7 @@ struct TcParams {
   int acc_slots;  // accumulator buffers: 2 lets the epilogue of a unit overlap the next main loop
   int external_reduce;  // cut tiles only store partial sums; splitk_reduce_kernel adds them
   const uint8_t* weight_low;
+  int prefetch_stages;  // K256 stages of weights the producer requests into L2 ahead of the ring (0 = none)
   const uint16_t* x;  // fused mode: 16-bit activations [tokens,k], quantised in the kernel (tokens <= 16); else null
   int x_bf16;
   uint32_t tmem_cols;
@@ -140,6 +151,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
       : "memory");
+}
+// Asks the TMA unit to bring one box of a tensor into L2; nothing is written to shared memory and no
+// barrier is involved.
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y)
+               : "memory");
 }
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -210,7 +228,11 @@ template <typename T>
 __device__ __forceinline__ void scatter_store(const OutTargets& out, int64_t index, float v) {
   const uint16_t bits = from_float<T>(v);
   out.ptr[0][index] = bits;
-  for (int w = 1; w < out.count; ++w) out.ptr[w][index] = bits;   // peers' receive buffers (NVLink stores)
+  if (out.count > 1) {   // peers' receive buffers (NVLink stores); indexes stay compile-time constants so
+#pragma unroll           // the pointers are read from the parameter bank, not from a local copy
+    for (int w = 1; w < HG_TP_MAX_WORLD; ++w)
+      if (w < out.count) out.ptr[w][index] = bits;
+  }
 }
 
 // Element offset of the half of the receive buffers this exchange writes (0 outside push mode).  Read
@@ -253,10 +275,13 @@ __device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-template <typename T>
-__global__ void __launch_bounds__(kTcThreads, 1)
+// FUSED = true adds the activation-quantiser warps (hg_run_x); the plain instantiation has none, so the
+// decode GEMMs on prepacked activations do not carry their threads and registers.
+template <typename T, bool FUSED>
+__global__ void __launch_bounds__(FUSED ? kTcThreads : kTcThreads - kQuantThreads, 1)
 hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant__ CUtensorMap map_high,
-                      const __grid_constant__ CUtensorMap map_act) {
+                      const __grid_constant__ CUtensorMap map_act, const __grid_constant__ CUtensorMap map_low,
+                      const __grid_constant__ CtaHeads heads) {
   pdl_trigger();  // the next kernel in the stream may start its own set-up
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -278,16 +303,25 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   // The schedule of this CTA is fetched before the set-up barrier so its latency overlaps the set-up.
-  const int unit_begin = p.cta_begin[blockIdx.x], unit_end = p.cta_begin[blockIdx.x + 1];
+  int unit_begin, unit_end;
   WorkUnit first_unit{};
-  if (unit_begin < unit_end) first_unit = p.units[unit_begin];
+  if (heads.valid) {
+    unit_begin = heads.begin[blockIdx.x];
+    unit_end = heads.begin[blockIdx.x + 1];
+    first_unit = heads.first[blockIdx.x];
+  } else {
+    unit_begin = p.cta_begin[blockIdx.x];
+    unit_end = p.cta_begin[blockIdx.x + 1];
+    if (unit_begin < unit_end) first_unit = p.units[unit_begin];
+  }
 
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_high)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_act)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_low)) : "memory");
     for (int s = 0; s < p.stages; ++s) {
       // TMA thread (with the byte count) + every loader thread (+ every quantiser thread in fused mode)
-      mbar_init(full_bar(s), 1 + kLoaderThreads + (p.x ? kQuantThreads : 0));
+      mbar_init(full_bar(s), 1 + kLoaderThreads + (FUSED ? kQuantThreads : 0));
       mbar_init(empty_bar(s), 1);                  // released by the MMA thread's commit
     }
     for (int s = 0; s < 2; ++s) {
@@ -328,7 +362,27 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
       uint32_t phase = 0;
       // Activations and their scales come from the previous kernel; the MXFP4 weight stream of the loader
       // warps does not and is already running.  (Fused mode: this thread only moves weights and their scales.)
-      if (!p.x) pdl_wait();
+      // L2 prefetch cursor: runs `prefetch_stages` K256 stages ahead of the ring over this CTA's unit list.
+      // Shared memory bounds the bytes the ring itself keeps in flight (four stages of MXFP4 are 64 KiB of
+      // HBM traffic per SM); requests parked in L2 cost no shared memory, and one TMA instruction of this
+      // thread fetches a whole 128-row box without touching the loader warps' LSU queue.
+      int pu = unit_begin, pkb = first_unit.kb_begin;
+      WorkUnit pw = first_unit;
+      auto prefetch_next = [&]() {
+        if (pu >= unit_end) return;
+        const int ppart = pw.tile >= p.tiles[0];
+        const int ptile = ppart ? pw.tile - p.tiles[0] : pw.tile;
+        if (ppart) {
+          tma_prefetch_2d(&map_high, pkb * kTileK, ptile * kTileRows);
+          if (pkb + 1 < pw.kb_end) tma_prefetch_2d(&map_high, (pkb + 1) * kTileK, ptile * kTileRows);
+        } else {
+          tma_prefetch_2d(&map_low, pkb * (kTileK / 2), ptile * kTileRows);   // 128 packed bytes per row = K256
+        }
+        pkb += 2;
+        if (pkb >= pw.kb_end && ++pu < unit_end) { pw = p.units[pu]; pkb = pw.kb_begin; }
+      };
+      for (int d = 0; d < p.prefetch_stages; ++d) prefetch_next();   // weights never depend on the previous kernel
+      if (!FUSED) pdl_wait();
       for (int u = unit_begin; u < unit_end && !error; ++u) {
         const WorkUnit wu = u == unit_begin ? first_unit : p.units[u];
         const int part = wu.tile >= p.tiles[0];
@@ -340,7 +394,7 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
           const int nkb = min(2, wu.kb_end - kb);
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { error = kErrProducer; break; }
           const uint32_t bar = full_bar(stage);
-          const bool fused = p.x != nullptr;  // activations and their scales are then produced by the loader warps
+          constexpr bool fused = FUSED;  // activations and their scales are then produced by the quantiser warps
           mbar_expect_tx(bar, uint32_t(nkb) * ((part ? 16384u : 0u) + (fused ? 512u : lay.b_tile + 1024u)));
           for (int i = 0; i < nkb; ++i) {
             if (part)
@@ -353,6 +407,7 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
           bulk_load(base + lay.sfa + uint32_t(stage) * 1024u, sfa_src + int64_t(kb) * 512, uint32_t(nkb) * 512u, bar);
           if (!fused)
             bulk_load(base + lay.sfb + uint32_t(stage) * 1024u, sfb_src + int64_t(kb) * 512, uint32_t(nkb) * 512u, bar);
+          if (p.prefetch_stages) prefetch_next();
           if (++stage == p.stages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -373,40 +428,33 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
     const int64_t pitch = p.k >> 1;  // bytes per packed row
     int stage = 0;
     uint32_t phase = 0;
-    int u = unit_begin;
-    WorkUnit wu = first_unit;
-    int kb = wu.kb_begin;
-    while (u < unit_end && !error) {
+    for (int u = unit_begin; u < unit_end && !error; ++u) {
+      const WorkUnit wu = u == unit_begin ? first_unit : p.units[u];
       const int part = wu.tile >= p.tiles[0];
-      const int nkb = min(2, wu.kb_end - kb);
-      bool ok = true;
-      if (lane == 0) ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag);
-      ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;
-      if (!ok) { error = kErrLoader; break; }
-      if (!part && blk < nkb) {
-        const int row0 = wu.tile * kTileRows + rsub;  // first row of this thread (low partition only)
-        const uint8_t* src = p.weight_low + int64_t(row0) * pitch + m * 8 + int64_t(kb) * 64;
-        const uint32_t dst = base + lay.a + uint32_t(stage) * 32768u + dst_off;
+      const int row0 = wu.tile * kTileRows + rsub;  // first row of this thread (low partition only)
+      const uint8_t* src0 = p.weight_low + int64_t(row0) * pitch + m * 8;
+      for (int kb = wu.kb_begin; kb < wu.kb_end; kb += 2) {
+        const int nkb = min(2, wu.kb_end - kb);
+        bool ok = true;
+        if (lane == 0) ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag);
+        ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;
+        if (!ok) { error = kErrLoader; break; }
+        if (!part && blk < nkb) {
+          const uint32_t dst = base + lay.a + uint32_t(stage) * 32768u + dst_off;
+          const uint8_t* src = src0 + int64_t(kb) * 64;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const bool valid = row0 + 8 * i < p.rows[0];
-          cp_async_8(dst + uint32_t(i) * 1024u, valid ? src + int64_t(8 * i) * pitch : p.weight_low, valid ? 8u : 0u);
+          for (int i = 0; i < 16; ++i) {
+            const bool valid = row0 + 8 * i < p.rows[0];
+            cp_async_8(dst + uint32_t(i) * 1024u, valid ? src + int64_t(8 * i) * pitch : p.weight_low, valid ? 8u : 0u);
+          }
         }
+        cp_async_arrive(full_bar(stage));
+        if (++stage == p.stages) { stage = 0; phase ^= 1u; }
       }
-      // Position of the next stage (next K256 of this unit, or the start of the next unit).
-      int next_u = u, next_kb = kb + 2;
-      WorkUnit next_wu = wu;
-      if (next_kb >= wu.kb_end) {
-        ++next_u;
-        if (next_u < unit_end) { next_wu = p.units[next_u]; next_kb = next_wu.kb_begin; }
-      }
-      cp_async_arrive(full_bar(stage));
-      if (++stage == p.stages) { stage = 0; phase ^= 1u; }
-      u = next_u; wu = next_wu; kb = next_kb;
     }
     // Copies still in flight must land before shared memory is released.
     asm volatile("cp.async.wait_all;" ::: "memory");
-  } else if (warp >= 13) {
+  } else if (FUSED && warp >= 13) {
     // ------------------------------------------------------------------ activation quantisers (warps 13..16)
     // Fused mode only (decode, at most 16 tokens; p.x != null).  Thread tq owns one K32 group (tq % 8) of
     // token tq / 8 in each K256 stage: same arithmetic as mx_quant_kernel, so codes and
@@ -414,7 +462,7 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
     // to the scale atom in shared memory and never touch HBM.  These warps issue no weight copies, so their
     // global loads do not queue behind HBM-latency cp.async traffic, and the NEXT stage's 64 bytes are
     // requested before the current ones are converted.
-    if (p.x) {
+    if constexpr (FUSED) {
       const int tq = threadIdx.x - 416;
       const int token = tq >> 3, blk_x = (tq & 7) >> 2, g = tq & 3;
       const uint16_t* x_row = p.x + int64_t(token) * p.k + g * 32;
@@ -500,6 +548,9 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
       uint32_t issued = 0;
       int acc_it = 0;
       uint32_t ring = 0;                                   // pipeline stages consumed by earlier units
+      const uint32_t issuer_mask = uint32_t(p.issuers) - 1u;
+      int ring_slot = 0;
+      uint32_t ring_round = 0;
       const uint32_t sf_base = sf_cols + uint32_t(q) * (8u * kScaleSets);
       uint32_t sf_flip = 0;
       for (int u = unit_begin; u < unit_end && !error; ++u, ++acc_it) {
@@ -516,14 +567,14 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
         // Ownership follows the ring SLOT of the global stage number g: issuer (g % stages) % issuers.  Each
         // ring slot, and with it each full/empty barrier, then has exactly one consumer that sees every round
         // in turn, so parity waits stay unambiguous however short units are.
+        // The ring depth is a multiple of the issuer count (a power of two), so (g % stages) % issuers is g % issuers.
         bool fresh = true;   // this issuer's accumulator has not been written in this unit yet
-        for (uint32_t l = 0; l < unit_stages && !error; ++l) {
-          if (((ring + l) % uint32_t(p.stages)) % uint32_t(p.issuers) != uint32_t(q)) continue;
+        for (uint32_t l = 0; l < unit_stages && !error; ++l, ring_slot = ring_slot + 1 == p.stages ? (ring_round ^= 1u, 0) : ring_slot + 1) {
+          if (((ring + l) & issuer_mask) != uint32_t(q)) continue;
           const int kb = wu.kb_begin + 2 * int(l);
           const int nkb = min(2, wu.kb_end - kb);
-          const uint32_t g = ring + l;
-          const int stage = int(g % uint32_t(p.stages));
-          if (!mbar_wait(full_bar(stage), (g / uint32_t(p.stages)) & 1u, abort_flag)) { error = kErrMmaFull; break; }
+          const int stage = ring_slot;   // (ring + l) % stages, kept incrementally with its round parity
+          if (!mbar_wait(full_bar(stage), ring_round, abort_flag)) { error = kErrMmaFull; break; }
           // The MXFP4 rows were written through the generic proxy (cp.async); the tensor core reads
           // shared memory through the async proxy.
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -578,8 +629,8 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
       // Issuers that owned a stage of this unit (global stages ring .. ring + unit_stages - 1, by ring slot).
       const uint32_t unit_stages = uint32_t(wu.kb_end - wu.kb_begin + 1) >> 1;
       uint32_t owners = 0;
-      for (uint32_t l = 0; l < unit_stages && l < uint32_t(p.stages); ++l)
-        owners |= 1u << (((ring + l) % uint32_t(p.stages)) % uint32_t(p.issuers));
+      for (uint32_t l = 0; l < unit_stages && l < uint32_t(p.issuers); ++l)
+        owners |= 1u << ((ring + l) & (uint32_t(p.issuers) - 1u));
       ring += unit_stages;
       const uint32_t taddr = tmem_base + lane_addr + uint32_t(slot) * acc_stride;
       float* ws = wu.nsplit > 1
@@ -600,12 +651,22 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
         }
         if (ws) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) ws[int64_t(c0 + i) * kTileRows] = r[i];
+          for (int i = 0; i < 16; ++i)
+            if (token0 + c0 + i < p.tokens) ws[int64_t(c0 + i) * kTileRows] = r[i];   // columns nobody will read are skipped
         } else if (row_ok) {
+          if (p.out.count == 1) {
+            uint16_t* column = p.out.ptr[0] + channel;
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int token = token0 + c0 + i;
-            if (token < p.tokens) scatter_store<T>(p.out, shift + int64_t(token) * p.outputs + channel, r[i]);
+            for (int i = 0; i < 16; ++i) {
+              const int token = token0 + c0 + i;
+              if (token < p.tokens) column[int64_t(token) * p.outputs] = from_float<T>(r[i]);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int token = token0 + c0 + i;
+              if (token < p.tokens) scatter_store<T>(p.out, shift + int64_t(token) * p.outputs + channel, r[i]);
+            }
           }
         }
       }
@@ -619,23 +680,38 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
         // all partials in K order.  No unit ever waits for another.
         epilogue_sync();
         if (threadIdx.x == 64) {
-          __threadfence();   // cumulative: covers the partials of all epilogue threads ordered by the barrier
-          *ticket_slot = atomicAdd(p.counters + wu.counter, 1);
+          // Release (cumulative over the partials of all epilogue threads, which the barrier ordered before
+          // this thread) and acquire in one instruction; the barrier below hands the acquired view on.
+          int ticket_value;
+          asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(ticket_value) : "l"(p.counters + wu.counter) : "memory");
+          *ticket_slot = ticket_value;
         }
         epilogue_sync();
         const int ticket = *ticket_slot;
         if (ticket == wu.nsplit - 1) {
-          __threadfence();
           const float* src = p.workspace + int64_t(wu.ws_slot) * (int64_t(p.n_tile) * kTileRows) + row_in_tile;
           if (row_ok) {
-            for (int c = 0; c < p.n_tile && token0 + c < p.tokens; c += 4) {
-              float sum[4] = {0.f, 0.f, 0.f, 0.f};
-              for (int s = 0; s < wu.nsplit; ++s) {
+            // Eight columns x four pieces per round: all loads of a round are in flight together (each is an
+            // L2 round trip), the additions keep K order.  Columns beyond the token count are not read.
+            for (int c = 0; c < p.n_tile && token0 + c < p.tokens; c += 8) {
+              float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+              for (int s0 = 0; s0 < wu.nsplit; s0 += 4) {
+                float v[4][8];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) sum[i] += __ldcg(src + (int64_t(s) * p.n_tile + c + i) * kTileRows);
+                for (int ds = 0; ds < 4; ++ds)
+#pragma unroll
+                  for (int i = 0; i < 8; ++i)
+                    v[ds][i] = (s0 + ds < wu.nsplit && token0 + c + i < p.tokens)
+                                   ? __ldcg(src + (int64_t(s0 + ds) * p.n_tile + c + i) * kTileRows) : 0.f;
+#pragma unroll
+                for (int ds = 0; ds < 4; ++ds)
+                  if (s0 + ds < wu.nsplit) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) sum[i] += v[ds][i];
+                  }
               }
 #pragma unroll
-              for (int i = 0; i < 4; ++i)
+              for (int i = 0; i < 8; ++i)
                 if (token0 + c + i < p.tokens)
                   scatter_store<T>(p.out, shift + int64_t(token0 + c + i) * p.outputs + channel, sum[i]);
             }
@@ -908,12 +984,22 @@ static EncodeTiled encode_tiled() {
 }
 
 // 2-D K-major tensor map over E4M3 bytes: dim0 = K, dim1 = rows; box = 128 x box_rows, 128B swizzle.
-static CUtensorMap make_map(const void* ptr, int rows, int k, int box_rows) {
+// K256 stages requested into L2 ahead of the shared-memory ring (HYGEMM_TC_PREFETCH; default 0 = off: measured
+// on B200 it does not shorten the ring's load-to-use time; gate_up M=16 19.7 us without, 21.0 us with 8 stages).
+static int prefetch_stages() {
+  static const int value = [] {
+    const char* text = std::getenv("HYGEMM_TC_PREFETCH");
+    return text ? std::max(0, std::min(64, std::atoi(text))) : 0;
+  }();
+  return value;
+}
+
+static CUtensorMap make_map(const void* ptr, int rows, int k, int box_rows, int box_inner = 128) {
   CUtensorMap map;
   std::memset(&map, 0, sizeof(map));
   const cuuint64_t dims[2] = {cuuint64_t(k), cuuint64_t(rows)};
   const cuuint64_t strides[1] = {cuuint64_t(k)};
-  const cuuint32_t box[2] = {128u, cuuint32_t(box_rows)};
+  const cuuint32_t box[2] = {cuuint32_t(box_inner), cuuint32_t(box_rows)};
   const cuuint32_t elem[2] = {1u, 1u};
   const CUresult r = encode_tiled()(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box,
                                     elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -922,8 +1008,20 @@ static CUtensorMap make_map(const void* ptr, int rows, int k, int box_rows) {
   return map;
 }
 
+static CtaHeads make_heads(const Plan& plan) {
+  CtaHeads heads{};
+  static const bool enabled = [] { const char* t = std::getenv("HYGEMM_TC_HEADS"); return !t || std::atoi(t) != 0; }();
+  if (plan.grid > kMaxHeads || !enabled) return heads;
+  heads.valid = 1;
+  for (int c = 0; c <= plan.grid; ++c) heads.begin[c] = plan.cta_begin[c];
+  for (int c = 0; c < plan.grid; ++c)
+    if (plan.cta_begin[c] < plan.cta_begin[c + 1]) heads.first[c] = plan.units[plan.cta_begin[c]];
+  return heads;
+}
+
 struct TcGemm {
   Plan plan;
+  CtaHeads heads{};
   int rows[2] = {0, 0}, tokens = 0, k = 0, outputs = 0, dtype = HG_DTYPE_BF16;
   WorkUnit* d_units = nullptr;
   int* d_cta_begin = nullptr;
@@ -956,7 +1054,9 @@ static void validate(const hg_problem& l, const hg_problem& h, bool fused = fals
 // handles with different stage counts can coexist.
 template <typename T>
 static void configure_kernel() {
-  check(cudaFuncSetAttribute(hybrid_gemm_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem),
+  check(cudaFuncSetAttribute(hybrid_gemm_tc_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem),
+        "cudaFuncSetAttribute");
+  check(cudaFuncSetAttribute(hybrid_gemm_tc_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem),
         "cudaFuncSetAttribute");
 }
 
@@ -971,6 +1071,7 @@ TcGemm* tc_create(const hg_problem& l, const hg_problem& h, int schedule, int dt
   g->rows[0] = l.rows; g->rows[1] = h.rows;
   g->tokens = any.tokens; g->k = any.k; g->outputs = any.outputs; g->dtype = dtype;
   g->plan = make_plan(l.rows, h.rows, any.tokens, any.k, sms, schedule);
+  g->heads = make_heads(g->plan);
   const Plan& plan = g->plan;
   check(cudaMalloc(&g->d_units, sizeof(WorkUnit) * std::max<size_t>(1, plan.units.size())), "cudaMalloc units");
   check(cudaMalloc(&g->d_cta_begin, sizeof(int) * plan.cta_begin.size()), "cudaMalloc schedule");
@@ -1053,6 +1154,7 @@ void tc_run(TcGemm* g, const hg_problem& l, const hg_problem& h, cudaStream_t st
   p.acc_slots = plan.acc_slots;
   p.external_reduce = plan.external_reduce ? 1 : 0;
   p.weight_low = static_cast<const uint8_t*>(l.weight);
+  p.prefetch_stages = prefetch_stages();
   p.x = static_cast<const uint16_t*>(x);
   p.x_bf16 = x_dtype == HG_DTYPE_BF16;
   p.units = g->d_units; p.cta_begin = g->d_cta_begin;
@@ -1061,10 +1163,18 @@ void tc_run(TcGemm* g, const hg_problem& l, const hg_problem& h, cudaStream_t st
   // never dereferenced.
   const CUtensorMap map_act = make_map(fused ? x : any.activation, any.tokens, any.k, plan.n_tile);
   const CUtensorMap map_high = h.rows ? make_map(h.weight, h.rows, h.k, kTileRows) : map_act;
-  if (g->dtype == HG_DTYPE_BF16)
-    check(launch_kernel(hybrid_gemm_tc_kernel<__nv_bfloat16>, dim3(plan.grid), dim3(kTcThreads), plan.smem_bytes, stream, p, map_high, map_act), "hybrid GEMM launch");
+  // Packed MXFP4 rows as bytes: one 128-byte x 128-row box is a K256 stage (used for L2 prefetch only).
+  const CUtensorMap map_low = l.rows ? make_map(l.weight, l.rows, l.k / 2, kTileRows, std::min(128, l.k / 2)) : map_act;
+  const dim3 grid(plan.grid), plain(kTcThreads - kQuantThreads), with_quantisers(kTcThreads);
+  const bool bf16 = g->dtype == HG_DTYPE_BF16;
+  cudaError_t launched;
+  if (fused)
+    launched = bf16 ? launch_kernel(hybrid_gemm_tc_kernel<__nv_bfloat16, true>, grid, with_quantisers, plan.smem_bytes, stream, p, map_high, map_act, map_low, g->heads)
+                    : launch_kernel(hybrid_gemm_tc_kernel<__half, true>, grid, with_quantisers, plan.smem_bytes, stream, p, map_high, map_act, map_low, g->heads);
   else
-    check(launch_kernel(hybrid_gemm_tc_kernel<__half>, dim3(plan.grid), dim3(kTcThreads), plan.smem_bytes, stream, p, map_high, map_act), "hybrid GEMM launch");
+    launched = bf16 ? launch_kernel(hybrid_gemm_tc_kernel<__nv_bfloat16, false>, grid, plain, plan.smem_bytes, stream, p, map_high, map_act, map_low, g->heads)
+                    : launch_kernel(hybrid_gemm_tc_kernel<__half, false>, grid, plain, plan.smem_bytes, stream, p, map_high, map_act, map_low, g->heads);
+  check(launched, "hybrid GEMM launch");
   launch_reduce(plan, p, g->d_cut, g->dtype, stream, true);
 }
 
@@ -1078,7 +1188,7 @@ const Plan& tc_plan(const TcGemm* g) { return g->plan; }
 
 void tc_kernel_attributes(int* registers, int* local_bytes) {
   cudaFuncAttributes attr{};
-  check(cudaFuncGetAttributes(&attr, hybrid_gemm_tc_kernel<__nv_bfloat16>), "cudaFuncGetAttributes");
+  check(cudaFuncGetAttributes(&attr, hybrid_gemm_tc_kernel<__nv_bfloat16, false>), "cudaFuncGetAttributes");
   *registers = attr.numRegs;
   *local_bytes = int(attr.localSizeBytes);
 }
@@ -1204,10 +1314,12 @@ void tc_run_static(int schedule, const hg_problem& l, const hg_problem& h, int d
   p.workspace = reinterpret_cast<float*>(base + off_work);
   const CUtensorMap map_act = make_map(any.activation, any.tokens, any.k, plan.n_tile);
   const CUtensorMap map_high = h.rows ? make_map(h.weight, h.rows, h.k, kTileRows) : map_act;
+  // Packed MXFP4 rows as bytes: one 128-byte x 128-row box is a K256 stage (used for L2 prefetch only).
+  const CUtensorMap map_low = l.rows ? make_map(l.weight, l.rows, l.k / 2, kTileRows, std::min(128, l.k / 2)) : map_act;
   if (dtype == HG_DTYPE_BF16)
-    hybrid_gemm_tc_kernel<__nv_bfloat16><<<plan.grid, kTcThreads, plan.smem_bytes, stream>>>(p, map_high, map_act);
+    hybrid_gemm_tc_kernel<__nv_bfloat16, false><<<plan.grid, kTcThreads - kQuantThreads, plan.smem_bytes, stream>>>(p, map_high, map_act, map_low, make_heads(plan));
   else
-    hybrid_gemm_tc_kernel<__half><<<plan.grid, kTcThreads, plan.smem_bytes, stream>>>(p, map_high, map_act);
+    hybrid_gemm_tc_kernel<__half, false><<<plan.grid, kTcThreads - kQuantThreads, plan.smem_bytes, stream>>>(p, map_high, map_act, map_low, make_heads(plan));
   check(cudaGetLastError(), "hybrid GEMM launch (static scratch)");
   launch_reduce(plan, p, reinterpret_cast<const int*>(base + off_cut), dtype, stream, false);
 }

@@ -1,0 +1,107 @@
+"""Fixed-batch decode benchmark of a random-init 7B-class model served by vLLM with the hybrid linear method.
+
+Counterpart of the reference's `integrations/vllm/formal/benchmark.py` (engine settings, uniform random
+token-id prompts, pure-decode timing through the worker extension) for models that exist only as an
+architecture: weights are vLLM's dummy initialisation, the MXFP8 channels of every linear are the 10 % of
+output channels with the largest weight-row L2 norm (quota rounded to 128), chosen at load time.
+
+    python -m hygemm_vllm.decode --arch qwen2.5-7b --batch 1,16,128 --prompt 128 --steps 128 [--dense]
+
+prints one JSON line per batch size: decode tokens/s over the span of the timed steps (engine gaps
+included), milliseconds per step and the audit of the hybrid layers.  `--dense` serves the same model with
+plain bf16 linears for comparison.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import tempfile
+from pathlib import Path
+
+ARCHITECTURES = {
+    "qwen2.5-7b": {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_size": 3584,
+                   "intermediate_size": 18944, "num_hidden_layers": 28, "num_attention_heads": 28,
+                   "num_key_value_heads": 4, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "vocab_size": 152064,
+                   "max_position_embeddings": 32768, "hidden_act": "silu", "tie_word_embeddings": False},
+    "mistral-7b": {"architectures": ["MistralForCausalLM"], "model_type": "mistral", "hidden_size": 4096,
+                   "intermediate_size": 14336, "num_hidden_layers": 32, "num_attention_heads": 32,
+                   "num_key_value_heads": 8, "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "vocab_size": 32000,
+                   "max_position_embeddings": 32768, "hidden_act": "silu", "tie_word_embeddings": False,
+                   "sliding_window": None},
+}
+
+
+def write_model_dir(folder, arch: str, dense: bool = False, fraction: float = 0.1, layers: int | None = None) -> Path:
+    """A model directory holding only `config.json` (served with `load_format="dummy"`)."""
+    config = dict(ARCHITECTURES[arch], torch_dtype="bfloat16")
+    if layers:
+        config["num_hidden_layers"] = layers
+    if not dense:
+        config["quantization_config"] = {"quant_method": "hygemm",
+                                         "selection": {"rule": "l2norm", "fraction": fraction, "multiple": 128}}
+    folder = Path(folder)
+    folder.mkdir(parents=True, exist_ok=True)
+    (folder / "config.json").write_text(json.dumps(config, indent=1))
+    return folder
+
+
+def engine_arguments(model_dir, batches, prompt: int, steps: int, dense: bool, tp: int = 1, memory: float = 0.6) -> dict:
+    """Keyword arguments of `vllm.LLM` (reference: formal/benchmark.py:44-49): no compilation, FULL CUDA graphs
+    captured for exactly the measured batch sizes after one eager warm-up each (the hybrid layers create their
+    GEMM handles in that warm-up)."""
+    return dict(model=str(model_dir), skip_tokenizer_init=True, load_format="dummy", dtype="bfloat16",
+                quantization=None if dense else "hygemm", max_model_len=prompt + steps + 16,
+                max_num_seqs=max(batches), max_num_batched_tokens=max(2048, prompt * 2),
+                gpu_memory_utilization=memory, tensor_parallel_size=tp, enable_prefix_caching=False, seed=0,
+                generation_config="vllm", worker_extension_cls="hygemm_vllm.worker.AuditWorkerExtension",
+                compilation_config={"mode": 0, "cudagraph_mode": "FULL", "cudagraph_capture_sizes": sorted(batches),
+                                    "max_cudagraph_capture_size": max(batches), "cudagraph_num_of_warmups": 1})
+
+
+def run(arch: str, batches, prompt: int, steps: int, dense: bool = False, layers: int | None = None, tp: int = 1):
+    import torch
+    os.environ.setdefault("VLLM_ENABLE_V1_MULTIPROCESSING", "0")   # engine in this process: the plugin is registered here
+    import hygemm_vllm
+    hygemm_vllm.register()
+    from vllm import LLM, SamplingParams
+    results = []
+    with tempfile.TemporaryDirectory() as tmp:
+        model_dir = write_model_dir(Path(tmp) / arch, arch, dense, layers=layers)
+        llm = LLM(**engine_arguments(model_dir, batches, prompt, steps, dense, tp))
+        vocab = ARCHITECTURES[arch]["vocab_size"]
+        sampling = SamplingParams(max_tokens=steps, ignore_eos=True, temperature=0.0, detokenize=False)
+        g = torch.Generator().manual_seed(20261024)
+        for batch in batches:
+            prompts = [{"prompt_token_ids": torch.randint(0, vocab, (prompt,), generator=g).tolist()} for _ in range(batch)]
+            llm.generate(prompts, sampling, use_tqdm=False)                      # warm-up pass
+            llm.collective_rpc("formal_begin", args=(batch,))
+            llm.generate(prompts, sampling, use_tqdm=False)
+            timing = llm.collective_rpc("formal_end")[0]
+            row = {"arch": arch, "dense": dense, "tp": tp, "batch": batch, "prompt": prompt, "steps": timing["steps"],
+                   "decode_tokens_per_s": batch * timing["steps"] / (timing["decode_span_ms"] * 1e-3),
+                   "decode_ms_per_step": timing["decode_ms_per_step"],
+                   "gpu_ms_per_step": timing["sum_step_gpu_ms"] / timing["steps"],
+                   "context": [timing["context_min"], timing["context_max"]], "graph_steps": timing["graph_steps"]}
+            results.append(row)
+            print(json.dumps(row), flush=True)
+        if not dense:
+            audit = llm.collective_rpc("hygemm_model_audit")[0]
+            print(json.dumps({"audit_layers": len(audit), "first": audit[0] if audit else None}), flush=True)
+    return results
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("--arch", default="qwen2.5-7b", choices=sorted(ARCHITECTURES))
+    ap.add_argument("--batch", default="1,16,128")
+    ap.add_argument("--prompt", type=int, default=128)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--layers", type=int, default=None, help="fewer decoder layers (smoke runs)")
+    ap.add_argument("--dense", action="store_true")
+    args = ap.parse_args(argv)
+    run(args.arch, [int(b) for b in args.batch.split(",")], args.prompt, args.steps, args.dense, args.layers)
+
+
+if __name__ == "__main__":
+    main()

