@@ -94,7 +94,9 @@ def test_a_step_outside_a_full_graph_is_refused(fakes):
     with pytest.raises(RuntimeError, match="No fixed-batch pure decode"):
         worker.formal_end()
     worker.formal_begin(1)
-    worker.execute_model(step(cached=[("a", 2)], tokens={"a": 1}))
+    worker.execute_model(step(new=[("b", 2)], tokens={"b": 2}))
+    worker.sample_tokens(None)
+    worker.execute_model(step(cached=[("b", 2)], tokens={"b": 1}))
     worker.sample_tokens(None)
     with pytest.raises(RuntimeError, match="did not use FULL Graph"):
         worker.formal_end()
