@@ -655,7 +655,7 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
             if (token0 + c0 + i < p.tokens) ws[int64_t(c0 + i) * kTileRows] = r[i];   // columns nobody will read are skipped
         } else if (row_ok) {
           if (p.out.count == 1) {
-            uint16_t* column = p.out.ptr[0] + channel;
+            uint16_t* column = p.out.ptr[0] + shift + channel;
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
               const int token = token0 + c0 + i;
