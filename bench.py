@@ -278,16 +278,52 @@ class Sweep:
             outs = self.run_m(i, m, self.dev[m], events)
         return outs
 
-    def step_e2e(self, host_out):
-        """Host buffers in, host buffers out: the call a user of the plugin-facing API makes."""
+    def step_e2e(self, host_out, overlap=False):
+        """Host buffers in, host buffers out: the call a user of the plugin-facing API makes.
+
+        `overlap`: the copies run on their own streams (inputs of every M are sent ahead, each M's results
+        leave while the next M computes); used when the step is captured into a CUDA graph, where every
+        tensor stays alive until the capture ends."""
         h2d = d2h = 0
+        if not overlap:
+            for i, m in enumerate(M_SWEEP):
+                x = {n: t.to(self.device, non_blocking=True) for n, t in self.host[m].items()}
+                h2d += sum(t.numel() * t.element_size() for t in self.host[m].values())
+                out = self.run_m(i, m, x)
+                for name in ("qkv", "o_proj", "down"):
+                    host_out[m][name].copy_(out[name], non_blocking=True)
+                    d2h += out[name].numel() * out[name].element_size()
+            return h2d, d2h
+        main = torch.cuda.current_stream()
+        if not hasattr(self, "copy_streams"):
+            self.copy_streams = (torch.cuda.Stream(), torch.cuda.Stream())
+        cin, cout = self.copy_streams
+        keep = []                                                  # nothing is freed (and reused) mid-capture
+        cin.wait_stream(main)
+        cout.wait_stream(main)
+        arrived = []
+        with torch.cuda.stream(cin):
+            for m in M_SWEEP:
+                x = {n: t.to(self.device, non_blocking=True) for n, t in self.host[m].items()}
+                h2d += sum(t.numel() * t.element_size() for t in self.host[m].values())
+                event = torch.cuda.Event()
+                event.record(cin)
+                arrived.append((x, event))
         for i, m in enumerate(M_SWEEP):
-            x = {n: t.to(self.device, non_blocking=True) for n, t in self.host[m].items()}
-            h2d += sum(t.numel() * t.element_size() for t in self.host[m].values())
+            x, event = arrived[i]
+            main.wait_event(event)
             out = self.run_m(i, m, x)
-            for name in ("qkv", "o_proj", "down"):
-                host_out[m][name].copy_(out[name], non_blocking=True)
-                d2h += out[name].numel() * out[name].element_size()
+            done = torch.cuda.Event()
+            done.record(main)
+            keep.append((x, out))
+            with torch.cuda.stream(cout):
+                cout.wait_event(done)
+                for name in ("qkv", "o_proj", "down"):
+                    host_out[m][name].copy_(out[name], non_blocking=True)
+                    d2h += out[name].numel() * out[name].element_size()
+        main.wait_stream(cin)
+        main.wait_stream(cout)
+        self.keep = keep
         return h2d, d2h
 
 
@@ -546,11 +582,35 @@ def main():
         h2d, d2h = sweep.step_e2e(host_out)
     stop.record()
     barrier()
-    e2e_ms = start.elapsed_time(stop)
+    e2e_eager_ms = start.elapsed_time(stop)
+    # The same calls, host buffers included, recorded once into a CUDA graph and replayed (what a serving
+    # engine does with the plugin): the copies become memcpy nodes on side streams and overlap the GEMMs.
+    e2e_graph, e2e_api = None, "hygemm_vllm.native.DualLinear.__call__ / producer.silu_pack + run_packed, eager"
+    e2e_ms = e2e_eager_ms
+    if graph is not None:
+        try:
+            e2e_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(e2e_graph):
+                h2d, d2h = sweep.step_e2e(host_out, overlap=True)
+            for _ in range(args.warmup):
+                e2e_graph.replay()
+            barrier()
+            start.record()
+            for _ in range(e2e_steps):
+                e2e_graph.replay()
+            stop.record()
+            barrier()
+            e2e_ms = start.elapsed_time(stop)
+            e2e_api = ("hygemm_vllm.native.DualLinear.__call__ / producer.silu_pack + run_packed with pinned host inputs "
+                       "and outputs, captured once into a CUDA graph (copies as memcpy nodes on side streams) and replayed")
+        except Exception as exc:
+            torch.cuda.synchronize()
+            e2e_graph, e2e_ms = None, e2e_eager_ms
+            e2e_api += f" (graph capture of the host-buffer step failed: {type(exc).__name__})"
     if world > 1:
-        t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
+        t = torch.tensor([e2e_ms, e2e_eager_ms], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = t.item()
+        e2e_ms, e2e_eager_ms = t.tolist()
     e2e_value = flops_step * e2e_steps / (e2e_ms * 1e-3) / 1e12
 
     # ---- per-launch GEMM durations in the same weight-cycling sequence: CUDA events recorded INSIDE a graph
@@ -623,8 +683,9 @@ def main():
                        "l2": "inputs larger than L2: two weight sets (272 MB) alternate between consecutive M",
                        "launch": note, "seed": SEED},
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps,
-                    "api": "hygemm_vllm.native.DualLinear.__call__ / producer.silu_pack + run_packed, eager"},
+                    "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps, "api": e2e_api,
+                    "eager_value": flops_step * e2e_steps / (e2e_eager_ms * 1e-3) / 1e12,
+                    "eager_ms_per_step": e2e_eager_ms / e2e_steps},
             "gpu_launches": sweep.launches_per_step * args.steps,
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
@@ -647,7 +708,7 @@ def main():
         # Graphs that captured NCCL kernels must go before the communicator; a watchdog ends the process
         # if the communicator teardown does not return (the result line is already printed and flushed).
         sys.stdout.flush()
-        graph = timed_graph = None  # noqa: F841
+        graph = timed_graph = e2e_graph = None  # noqa: F841
         torch.cuda.synchronize()
         watchdog = threading.Timer(30.0, os._exit, args=(0,))
         watchdog.daemon = True
