@@ -140,8 +140,13 @@ def build_layer(device, layer_seed: int, rank: int, world: int):
             else:
                 keep, offset = [], 0
                 for width in parts.values():
-                    step = width // world
-                    keep.append(torch.arange(offset + rank * step, offset + (rank + 1) * step))
+                    if name == "gate_up":
+                        # gate and up keep the intermediate channels of this rank's K shard of down_proj (whole
+                        # K128 blocks, uneven when 148 blocks do not divide by the world size)
+                        begin, end = k_block_shard(width, rank, world)
+                    else:
+                        begin, end = rank * (width // world), (rank + 1) * (width // world)
+                    keep.append(torch.arange(offset + begin, offset + end))
                     offset += width
                 keep = torch.cat(keep)
                 mask = torch.zeros(n, dtype=torch.bool)

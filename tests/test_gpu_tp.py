@@ -115,3 +115,32 @@ def test_missing_peer_ends_the_wait_with_a_status():
     assert ex.status() == 0
     assert (out == 7.0).all() and ex.state[0].item() == 1
     assert torch.ones(4, device="cuda").sum().item() == 4.0
+
+
+def test_bench_shards_stay_consistent_at_eight_ranks():
+    """The benchmark's tensor-parallel shards: gate_up keeps exactly the intermediate channels of the rank's
+    K shard of down_proj (whole K128 blocks, uneven at 8 ranks), so the SwiGLU producer feeds down_proj."""
+    import importlib.util
+    import sys
+    from pathlib import Path
+    from hygemm_vllm import producer
+    spec = importlib.util.spec_from_file_location("bench_module", Path(__file__).resolve().parent.parent / "bench.py")
+    bench = importlib.util.module_from_spec(spec)
+    argv, sys.argv = sys.argv, ["bench.py"]
+    try:
+        spec.loader.exec_module(bench)
+    finally:
+        sys.argv = argv
+    total = 0
+    for rank in (0, 3, 7):
+        layer = bench.build_layer(torch.device("cuda", 0), bench.SEED, rank, 8)
+        assert layer["gate_up"].outputs == 2 * layer["down"].k and layer["down"].k % 128 == 0
+        assert layer["o_proj"].k % 128 == 0 and layer["qkv"].outputs == 4608 // 8
+        x = torch.randn(16, 3584, dtype=torch.bfloat16, device="cuda")
+        q, sf = producer.silu_pack(layer["gate_up"](x), 0)
+        y = layer["down"].run_packed(q, sf)
+        assert y.shape == (16, 3584) and torch.isfinite(y.float()).all()
+        total += layer["down"].k
+        for rt in layer.values():
+            rt.close()
+    assert total in (2432 + 2432 + 2304, 2432 * 2 + 2304, 2432 + 2304 * 2)
