@@ -59,9 +59,31 @@ def engine_arguments(model_dir, batches, prompt: int, steps: int, dense: bool, t
                                     "max_cudagraph_capture_size": max(batches), "cudagraph_num_of_warmups": 1})
 
 
+def ensure_plugin_entry_point() -> None:
+    """vLLM loads `vllm.general_plugins` entry points in every worker process.  When this package is used from
+    its source tree (not pip-installed) no entry point exists, so one is published the way an editable install
+    would: a `*.dist-info` with `entry_points.txt` in a temporary directory that, together with the package
+    root, is put on `PYTHONPATH` for the worker processes."""
+    import importlib.metadata as metadata
+    import sys
+    if any(ep.name == "hygemm_quantization" for ep in metadata.entry_points(group="vllm.general_plugins")):
+        return
+    root = Path(tempfile.mkdtemp(prefix="hygemm_plugin_"))
+    info = root / "hygemm_vllm_b200-0.1.dist-info"
+    info.mkdir()
+    (info / "METADATA").write_text("Metadata-Version: 2.1\nName: hygemm-vllm-b200\nVersion: 0.1\n")
+    (info / "entry_points.txt").write_text("[vllm.general_plugins]\nhygemm_quantization = hygemm_vllm:register\n")
+    package_root = str(Path(__file__).resolve().parent.parent)
+    os.environ["PYTHONPATH"] = os.pathsep.join(p for p in (str(root), package_root, os.environ.get("PYTHONPATH", "")) if p)
+    sys.path.insert(0, str(root))
+
+
 def run(arch: str, batches, prompt: int, steps: int, dense: bool = False, layers: int | None = None, tp: int = 1):
     import torch
-    os.environ.setdefault("VLLM_ENABLE_V1_MULTIPROCESSING", "0")   # engine in this process: the plugin is registered here
+    if tp == 1:
+        os.environ.setdefault("VLLM_ENABLE_V1_MULTIPROCESSING", "0")   # engine in this process: the plugin is registered here
+    else:
+        ensure_plugin_entry_point()                                    # worker processes find the plugin themselves
     import hygemm_vllm
     hygemm_vllm.register()
     from vllm import LLM, SamplingParams
@@ -99,8 +121,9 @@ def main(argv=None):
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--layers", type=int, default=None, help="fewer decoder layers (smoke runs)")
     ap.add_argument("--dense", action="store_true")
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size (one worker process per GPU)")
     args = ap.parse_args(argv)
-    run(args.arch, [int(b) for b in args.batch.split(",")], args.prompt, args.steps, args.dense, args.layers)
+    run(args.arch, [int(b) for b in args.batch.split(",")], args.prompt, args.steps, args.dense, args.layers, args.tp)
 
 
 if __name__ == "__main__":
