@@ -176,20 +176,25 @@ class DualLinear:
         y = torch.empty((tokens, self.outputs), dtype=self.dtype, device=x.device)
         low, high, _, low_ref, high_ref = self._rebound(tokens, x, x, y)
         stream = _stream(x.device)
-        key = (tokens, self.low_id, self.high_id, self.lo.numel(), self.hi.numel())
-        handle = self.handles.get(key)
-        if handle is None:
-            if torch.cuda.is_current_stream_capturing():
-                raise RuntimeError(f"HyGEMM shape T={key} must be warmed before graph capture")
-            handle = C.c_void_p()
-            check(library().hg_create_dtype(self.low_id, self.high_id, low_ref, high_ref, stream,
-                                            DTYPES[self.dtype], C.byref(handle)))
-            self.handles[key] = handle
+        handle = self._handle(tokens, self.low_id, self.high_id, low_ref, high_ref, stream)
         status = _lib.hg_run_x(handle, low_ref, high_ref, x.data_ptr(), DTYPES[x.dtype], stream)
         if status:
             check(status)
         self.calls[tokens] = self.calls.get(tokens, 0) + 1
         return y
+
+    def _handle(self, tokens, low_id, high_id, low_ref, high_ref, stream):
+        """GEMM handle of one (token count, schedule ids) pair, created on first use: never during stream
+        capture, where an unseen shape is an error (reference: native.py:95-104)."""
+        key = (tokens, low_id, high_id, self.lo.numel(), self.hi.numel())
+        handle = self.handles.get(key)
+        if handle is None:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError(f"HyGEMM shape T={key} must be warmed before graph capture")
+            handle = C.c_void_p()
+            check(library().hg_create_dtype(low_id, high_id, low_ref, high_ref, stream, DTYPES[self.dtype], C.byref(handle)))
+            self.handles[key] = handle
+        return handle
 
     def problems(self, q, sf, y):
         """The two `Problem` structs of a call (shared activation, scales and output pointers)."""
@@ -233,15 +238,7 @@ class DualLinear:
             plan = self.plans.get(self.outputs, self.k, self.hi.numel(), tokens)
             low_id, high_id, policy = plan["low_id"], plan["high_id"], POLICIES[plan["policy"]]
             self.plans_used[tokens] = [plan["tokens"], low_id, high_id, policy]
-        key = (tokens, low_id, high_id, self.lo.numel(), self.hi.numel())
-        handle = self.handles.get(key)
-        if handle is None:
-            if torch.cuda.is_current_stream_capturing():
-                raise RuntimeError(f"HyGEMM shape T={key} must be warmed before graph capture")
-            handle = C.c_void_p()
-            check(library().hg_create_dtype(low_id, high_id, low_ref, high_ref, stream,
-                                            DTYPES[self.dtype], C.byref(handle)))
-            self.handles[key] = handle
+        handle = self._handle(tokens, low_id, high_id, low_ref, high_ref, stream)
         status = _lib.hg_run(handle, low_ref, high_ref, stream, policy)
         if status:
             check(status)
@@ -269,15 +266,7 @@ class DualLinear:
         y = torch.empty((tokens, self.outputs), dtype=self.dtype, device=src.device)
         low, high, _, low_ref, high_ref = self._rebound(tokens, src, src if fused else sf, y)
         stream = _stream(src.device)
-        key = (tokens, self.low_id, self.high_id, self.lo.numel(), self.hi.numel())
-        handle = self.handles.get(key)
-        if handle is None:
-            if torch.cuda.is_current_stream_capturing():
-                raise RuntimeError(f"HyGEMM shape T={key} must be warmed before graph capture")
-            handle = C.c_void_p()
-            check(library().hg_create_dtype(self.low_id, self.high_id, low_ref, high_ref, stream,
-                                            DTYPES[self.dtype], C.byref(handle)))
-            self.handles[key] = handle
+        handle = self._handle(tokens, self.low_id, self.high_id, low_ref, high_ref, stream)
         lib = library()
         check(lib.hg_run_push(handle, low_ref, high_ref, x.data_ptr() if fused else None,
                               DTYPES[x.dtype] if fused else 0, exchange.recv_ptrs, exchange.world, exchange.rank,
