@@ -64,7 +64,7 @@ def run_codec(binary: Path, kind: str, values: np.ndarray) -> np.ndarray:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="root of the reference checkout")
     args = ap.parse_args()
     ref = Path(args.reference) / "integrations" / "vllm"
     sys.path.insert(0, str(ref))
