@@ -50,7 +50,7 @@ def buffers(world, slot, dtype):
     return recv, flags
 
 
-@pytest.mark.parametrize("tokens,fused", [(1, True), (16, True), (16, False), (48, False), (130, False)])
+@pytest.mark.parametrize("tokens,fused", [(1, True), (16, True), (16, False), (48, False), (100, False), (128, False), (130, False)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_two_emulated_ranks_sum_bit_exact(tokens, fused, dtype):
     world, k, outputs, high = 2, 1024, 640, 96
