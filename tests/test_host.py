@@ -212,3 +212,26 @@ def test_exchange_arguments_are_checked():
     assert b"multiples of 8" in lib.hg_last_error()
     assert lib.hg_tp_reduce(16, 16, 8, 8, 9, 0, flags, 16, 1, None) == -1
     assert lib.hg_run_push(None, None, None, None, 0, None, 2, 0, 8, None, None) == -1
+
+
+def test_tuner_candidates_and_plan_binding(tmp_path):
+    """The tuner's search space and the bound plan document (no GPU): schedules 1-3, the SIMT pair policies up
+    to four tokens, and a binding that `PlanTable` accepts for this library and refuses for another."""
+    from hygemm_vllm import tune
+    assert [c["low_id"] for c in tune.candidates(16)] == [1, 2, 3]
+    small = tune.candidates(4)
+    assert [c["policy"] for c in small[3:]] == ["gemv_pair1", "gemv_pair2", "gemv_pair4"] and all(c["low_id"] == 28 for c in small[3:])
+    rows = [{"out": 640, "k": 512, "high": 64, "tokens": t, "low_id": 3, "high_id": 3, "policy": "serial"} for t in (8, 128)]
+    document = tune.bind(rows)
+    assert document["binding"]["layout"] == plans.LAYOUT and len(document["binding"]["library_sha256"]) == 64
+    path = tmp_path / "plan.json"
+    path.write_text(json.dumps(document))
+    table = plans.PlanTable(path, "hygemm")
+    assert table.get(640, 512, 64, 9)["tokens"] == 128 and table.get(640, 512, 64, 1)["tokens"] == 8
+    with pytest.raises(ValueError, match="exceeds tuned buckets"):
+        table.get(640, 512, 64, 129)
+    other = tmp_path / "other.so"
+    other.write_bytes(b"not this library")
+    path.write_text(json.dumps(tune.bind(rows, other)))
+    with pytest.raises(ValueError, match="different binary"):
+        plans.PlanTable(path, "hygemm")
