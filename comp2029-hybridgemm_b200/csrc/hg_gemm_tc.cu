@@ -20,13 +20,21 @@
 // * Scales: the 512-byte atoms (128 rows x 4 K32 groups) go to TMEM with
 //   tcgen05.cp 32x128b.warpx4; the byte of the current K32 block is selected
 //   with the a_sf_id/b_sf_id descriptor fields.
-// * Issue: up to four MMA-issuing threads in separate warps, each owning every
-//   I-th pipeline stage and its own accumulator (a tcgen05 instruction costs
-//   its issuer ~100 cycles whatever its shape).
+// * Issue: up to four MMA-issuing threads in separate warps (two by default up
+//   to 64-token tiles, one at 128), each owning every I-th pipeline stage and
+//   its own accumulator: a tcgen05 instruction costs its issuing thread 50-430
+//   cycles whatever its shape (MMA 90, scale copy 51, commit 432) and threads
+//   issue in parallel.
+// * Decode sizes (at most 16 tokens) can quantise their activations in the
+//   launch: the FUSED instantiation adds four quantiser warps (hg_run_x).
+// * Row-parallel tensor parallelism: the epilogue can store each result into a
+//   slot of every peer's receive buffer over NVLink (hg_run_push); hg_tp.cu
+//   holds the wait-and-sum kernel.
 // * Schedule: a host-built list of work units (row tile, token tile, K range)
 //   per CTA: data-parallel, split-K or stream-K.  Tiles cut along K write fp32
-//   partials to a workspace; the LAST unit to arrive (atomic ticket, no
-//   spinning) sums the partials in K order, so the result is deterministic.
+//   partials to a workspace; up to 48-token tiles the LAST unit to arrive
+//   (one acq_rel ticket, no spinning) sums the partials in K order, wider
+//   tiles are summed by splitk_reduce_kernel; either way deterministic.
 // * Epilogue: tcgen05.ld 32x32b, accumulators added in a fixed order, fp32 ->
 //   bf16/fp16 (RNE), scattered straight to out[t*N + ids[r]]; consecutive lanes
 //   own consecutive rows, so sorted maps give contiguous 64-byte runs.  Two
@@ -567,7 +575,7 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
         // Ownership follows the ring SLOT of the global stage number g: issuer (g % stages) % issuers.  Each
         // ring slot, and with it each full/empty barrier, then has exactly one consumer that sees every round
         // in turn, so parity waits stay unambiguous however short units are.
-        // The ring depth is a multiple of the issuer count (a power of two), so (g % stages) % issuers is g % issuers.
+        // The ring depth is a multiple of the issuer count (1, 2 or 4), so (g % stages) % issuers is g % issuers.
         bool fresh = true;   // this issuer's accumulator has not been written in this unit yet
         for (uint32_t l = 0; l < unit_stages && !error; ++l, ring_slot = ring_slot + 1 == p.stages ? (ring_round ^= 1u, 0) : ring_slot + 1) {
           if (((ring + l) & issuer_mask) != uint32_t(q)) continue;

@@ -93,7 +93,7 @@ int hg_create_dtype(int low_id, int high_id, const hg_problem* low, const hg_pro
  * enqueue on `stream`; allocates nothing; may be captured in a CUDA graph. */
 int hg_run(void* handle, const hg_problem* low, const hg_problem* high, void* stream, int policy);
 /* hg_pack + hg_run in ONE launch for decode sizes (tokens <= 16): `x` is the 16-bit activation matrix
- * [tokens,k] (x_dtype = HG_DTYPE_*); the loader warps of the GEMM kernel quantise each CTA's K slice with
+ * [tokens,k] (x_dtype = HG_DTYPE_*); dedicated quantiser warps of the GEMM kernel convert each CTA's K slice with
  * the arithmetic of hg_pack, so the output equals hg_pack followed by hg_run bit for bit, without the
  * quantiser launch and without the codes and scales passing through HBM.  The problems' `activation` and
  * `activation_scales` are ignored (may be null).  No counterpart in the reference, which always runs its
