@@ -27,9 +27,10 @@
 //   issue in parallel.
 // * Decode sizes (at most 16 tokens) can quantise their activations in the
 //   launch: the FUSED instantiation adds four quantiser warps (hg_run_x).
-// * Row-parallel tensor parallelism: the epilogue can store each result into a
-//   slot of every peer's receive buffer over NVLink (hg_run_push); hg_tp.cu
-//   holds the wait-and-sum kernel.
+// * Row-parallel tensor parallelism: the epilogue can store the partial result
+//   (fp32 for decode sizes) into this rank's half of a peer-mapped exchange
+//   buffer (hg_run_partial); hg_tp.cu holds the kernel that pulls every rank's
+//   partial over NVLink and adds them.
 // * Schedule: a host-built list of work units (row tile, token tile, K range)
 //   per CTA: data-parallel, split-K or stream-K.  Tiles cut along K write fp32
 //   partials to a workspace; up to 48-token tiles the LAST unit to arrive
@@ -57,14 +58,15 @@ namespace hg {
 // Device side
 // ---------------------------------------------------------------------------------------------
 
-// Where the epilogue stores.  Outside tensor-parallel push mode there is one target.  In push mode
-// (hg_run_push) `ptr[w]` is slot `rank` of rank w's receive buffer, `epoch` the device word counting
-// finished exchanges and `parity_stride` the distance in elements between the two halves of a receive buffer.
+// Where the epilogue stores: `ptr` is [tokens, outputs] of 16-bit elements, or of fp32 when `f32` is set.
+// For a row-parallel partial (hg_run_partial) `ptr` is this rank's exchange buffer, `epoch` the device word
+// that counts finished exchanges and `parity_bytes` the distance between the two halves of the buffer; the
+// half written is the one of exchange `*epoch + 1`.
 struct OutTargets {
-  uint16_t* ptr[HG_TP_MAX_WORLD];
-  int count;
+  void* ptr;
+  int f32;
   const int* epoch;
-  int64_t parity_stride;
+  int64_t parity_bytes;
 };
 
 // Per-CTA start of the schedule, passed BY VALUE as a kernel parameter: a CTA learns its first work unit
@@ -90,7 +92,6 @@ struct TcParams {
   int acc_slots;  // accumulator buffers: 2 lets the epilogue of a unit overlap the next main loop
   int external_reduce;  // cut tiles only store partial sums; splitk_reduce_kernel adds them
   const uint8_t* weight_low;
-  int prefetch_stages;  // K256 stages of weights the producer requests into L2 ahead of the ring (0 = none)
   const uint16_t* x;  // fused mode: 16-bit activations [tokens,k], quantised in the kernel (tokens <= 16); else null
   int x_bf16;
   uint32_t tmem_cols;
@@ -160,13 +161,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
-// Asks the TMA unit to bring one box of a tensor into L2; nothing is written to shared memory and no
-// barrier is involved.
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, int y) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];"
-               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y)
-               : "memory");
-}
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
@@ -233,22 +227,18 @@ __device__ __forceinline__ bool epilogue_all(bool ok) {
 __device__ __forceinline__ void epilogue_sync() { asm volatile("barrier.cta.sync 1, 128;" ::: "memory"); }
 
 template <typename T>
-__device__ __forceinline__ void scatter_store(const OutTargets& out, int64_t index, float v) {
-  const uint16_t bits = from_float<T>(v);
-  out.ptr[0][index] = bits;
-  if (out.count > 1) {   // peers' receive buffers (NVLink stores); indexes stay compile-time constants so
-#pragma unroll           // the pointers are read from the parameter bank, not from a local copy
-    for (int w = 1; w < HG_TP_MAX_WORLD; ++w)
-      if (w < out.count) out.ptr[w][index] = bits;
-  }
+__device__ __forceinline__ void scatter_store(const OutTargets& out, char* base, int64_t index, float v) {
+  if (out.f32) reinterpret_cast<float*>(base)[index] = v;
+  else reinterpret_cast<uint16_t*>(base)[index] = from_float<T>(v);
 }
 
-// Element offset of the half of the receive buffers this exchange writes (0 outside push mode).  Read
-// after pdl_wait(): the word is advanced by the reduce kernel of the previous exchange.
-__device__ __forceinline__ int64_t out_shift(const OutTargets& out) {
-  if (!out.epoch) return 0;
+// Start of the output this launch writes: the plain output, or the half of the exchange buffer that belongs
+// to the coming exchange.  Read after pdl_wait(): the word is advanced by the kernel that ends the previous exchange.
+__device__ __forceinline__ char* out_base(const OutTargets& out) {
+  char* base = static_cast<char*>(out.ptr);
+  if (!out.epoch) return base;
   const int e = *reinterpret_cast<const volatile int*>(out.epoch) + 1;
-  return int64_t(e & 1) * out.parity_stride;
+  return base + int64_t(e & 1) * out.parity_bytes;
 }
 
 // Shared-memory plan.  One pipeline stage covers up to two K128 blocks (K256):
@@ -288,8 +278,7 @@ __device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
 template <typename T, bool FUSED>
 __global__ void __launch_bounds__(FUSED ? kTcThreads : kTcThreads - kQuantThreads, 1)
 hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant__ CUtensorMap map_high,
-                      const __grid_constant__ CUtensorMap map_act, const __grid_constant__ CUtensorMap map_low,
-                      const __grid_constant__ CtaHeads heads) {
+                      const __grid_constant__ CUtensorMap map_act, const __grid_constant__ CtaHeads heads) {
   pdl_trigger();  // the next kernel in the stream may start its own set-up
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -324,9 +313,9 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
   }
 
   if (threadIdx.x == 0) {
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_high)) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_act)) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_low)) : "memory");
+    // a map the launch does not use (no MXFP8 rows; activations quantised in the kernel) arrives as zeros
+    if (p.rows[1]) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_high)) : "memory");
+    if (!FUSED) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_act)) : "memory");
     for (int s = 0; s < p.stages; ++s) {
       // TMA thread (with the byte count) + every loader thread (+ every quantiser thread in fused mode)
       mbar_init(full_bar(s), 1 + kLoaderThreads + (FUSED ? kQuantThreads : 0));
@@ -370,26 +359,6 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
       uint32_t phase = 0;
       // Activations and their scales come from the previous kernel; the MXFP4 weight stream of the loader
       // warps does not and is already running.  (Fused mode: this thread only moves weights and their scales.)
-      // L2 prefetch cursor: runs `prefetch_stages` K256 stages ahead of the ring over this CTA's unit list.
-      // Shared memory bounds the bytes the ring itself keeps in flight (four stages of MXFP4 are 64 KiB of
-      // HBM traffic per SM); requests parked in L2 cost no shared memory, and one TMA instruction of this
-      // thread fetches a whole 128-row box without touching the loader warps' LSU queue.
-      int pu = unit_begin, pkb = first_unit.kb_begin;
-      WorkUnit pw = first_unit;
-      auto prefetch_next = [&]() {
-        if (pu >= unit_end) return;
-        const int ppart = pw.tile >= p.tiles[0];
-        const int ptile = ppart ? pw.tile - p.tiles[0] : pw.tile;
-        if (ppart) {
-          tma_prefetch_2d(&map_high, pkb * kTileK, ptile * kTileRows);
-          if (pkb + 1 < pw.kb_end) tma_prefetch_2d(&map_high, (pkb + 1) * kTileK, ptile * kTileRows);
-        } else {
-          tma_prefetch_2d(&map_low, pkb * (kTileK / 2), ptile * kTileRows);   // 128 packed bytes per row = K256
-        }
-        pkb += 2;
-        if (pkb >= pw.kb_end && ++pu < unit_end) { pw = p.units[pu]; pkb = pw.kb_begin; }
-      };
-      for (int d = 0; d < p.prefetch_stages; ++d) prefetch_next();   // weights never depend on the previous kernel
       if (!FUSED) pdl_wait();
       for (int u = unit_begin; u < unit_end && !error; ++u) {
         const WorkUnit wu = u == unit_begin ? first_unit : p.units[u];
@@ -415,7 +384,6 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
           bulk_load(base + lay.sfa + uint32_t(stage) * 1024u, sfa_src + int64_t(kb) * 512, uint32_t(nkb) * 512u, bar);
           if (!fused)
             bulk_load(base + lay.sfb + uint32_t(stage) * 1024u, sfb_src + int64_t(kb) * 512, uint32_t(nkb) * 512u, bar);
-          if (p.prefetch_stages) prefetch_next();
           if (++stage == p.stages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -621,7 +589,7 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
     int acc_it = 0, stored = 0;
     uint32_t ring = 0;
     pdl_wait();  // nothing is written to global memory before every earlier kernel has finished
-    const int64_t shift = out_shift(p.out);
+    char* const out = out_base(p.out);
     for (int u = unit_begin; u < unit_end; ++u, ++acc_it) {
       const WorkUnit wu = u == unit_begin ? first_unit : p.units[u];
       const int part = wu.tile >= p.tiles[0];
@@ -662,18 +630,19 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
           for (int i = 0; i < 16; ++i)
             if (token0 + c0 + i < p.tokens) ws[int64_t(c0 + i) * kTileRows] = r[i];   // columns nobody will read are skipped
         } else if (row_ok) {
-          if (p.out.count == 1) {
-            uint16_t* column = p.out.ptr[0] + shift + channel;
+          if (!p.out.f32) {
+            uint16_t* column = reinterpret_cast<uint16_t*>(out) + channel;
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
               const int token = token0 + c0 + i;
               if (token < p.tokens) column[int64_t(token) * p.outputs] = from_float<T>(r[i]);
             }
           } else {
+            float* column = reinterpret_cast<float*>(out) + channel;
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
               const int token = token0 + c0 + i;
-              if (token < p.tokens) scatter_store<T>(p.out, shift + int64_t(token) * p.outputs + channel, r[i]);
+              if (token < p.tokens) column[int64_t(token) * p.outputs] = r[i];
             }
           }
         }
@@ -721,7 +690,7 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
 #pragma unroll
               for (int i = 0; i < 8; ++i)
                 if (token0 + c + i < p.tokens)
-                  scatter_store<T>(p.out, shift + int64_t(token0 + c + i) * p.outputs + channel, sum[i]);
+                  scatter_store<T>(p.out, out, int64_t(token0 + c + i) * p.outputs + channel, sum[i]);
             }
           }
           if (threadIdx.x == 64) p.counters[wu.counter] = 0;  // ready for the next launch
@@ -775,7 +744,7 @@ splitk_reduce_kernel(const ReduceParams rp) {
   const int row = (part ? tile_v - rp.tiles[0] : tile_v) * kTileRows + int(threadIdx.x);
   if (row >= rp.rows[part]) return;
   const int channel = rp.ids[part][row];
-  const int64_t shift = out_shift(rp.out);
+  char* const out = out_base(rp.out);
   const int token0 = token_tile * rp.n_tile + c0;
   const float* src = rp.workspace + int64_t(slot) * (int64_t(rp.n_tile) * kTileRows) + int64_t(c0) * kTileRows + threadIdx.x;
   float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -785,7 +754,7 @@ splitk_reduce_kernel(const ReduceParams rp) {
   }
 #pragma unroll
   for (int i = 0; i < 8; ++i)
-    if (token0 + i < rp.tokens) scatter_store<T>(rp.out, shift + int64_t(token0 + i) * rp.outputs + channel, sum[i]);
+    if (token0 + i < rp.tokens) scatter_store<T>(rp.out, out, int64_t(token0 + i) * rp.outputs + channel, sum[i]);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -812,6 +781,9 @@ Plan make_plan(int rows_low, int rows_high, int tokens, int k, int sms, int sche
     if (capped >= 64 || tokens <= capped) plan.n_tile = capped;
   }
   plan.token_tiles = (tokens + plan.n_tile - 1) / plan.n_tile;
+  // A tile's activation scales sit in TMEM column (token0 % 128) / 32 of their atom; an odd column there made
+  // the MMA raise "misaligned address", so token tiles narrower than 64 must be alone in the call.
+  if (plan.n_tile < 64 && plan.token_tiles > 1) throw std::runtime_error("Token tiles narrower than 64 cannot share a scale atom");
   const int stage_bytes = 32768 + 2 * plan.n_tile * 128 + 2048;  // one K256 stage: weights, activations, scales
   plan.stages = std::min(kMaxStages, (kMaxDynamicSmem - 1024 - kBarrierBytes) / stage_bytes);
   if (const char* cap = std::getenv("HYGEMM_TC_STAGES"))  // tuning aid: cap the pipeline depth
@@ -1003,22 +975,12 @@ static EncodeTiled encode_tiled() {
 }
 
 // 2-D K-major tensor map over E4M3 bytes: dim0 = K, dim1 = rows; box = 128 x box_rows, 128B swizzle.
-// K256 stages requested into L2 ahead of the shared-memory ring (HYGEMM_TC_PREFETCH; default 0 = off: measured
-// on B200 it does not shorten the ring's load-to-use time; gate_up M=16 19.7 us without, 21.0 us with 8 stages).
-static int prefetch_stages() {
-  static const int value = [] {
-    const char* text = std::getenv("HYGEMM_TC_PREFETCH");
-    return text ? std::max(0, std::min(64, std::atoi(text))) : 0;
-  }();
-  return value;
-}
-
-static CUtensorMap make_map(const void* ptr, int rows, int k, int box_rows, int box_inner = 128) {
+static CUtensorMap make_map(const void* ptr, int rows, int k, int box_rows) {
   CUtensorMap map;
   std::memset(&map, 0, sizeof(map));
   const cuuint64_t dims[2] = {cuuint64_t(k), cuuint64_t(rows)};
   const cuuint64_t strides[1] = {cuuint64_t(k)};
-  const cuuint32_t box[2] = {cuuint32_t(box_inner), cuuint32_t(box_rows)};
+  const cuuint32_t box[2] = {128u, cuuint32_t(box_rows)};
   const cuuint32_t elem[2] = {1u, 1u};
   const CUresult r = encode_tiled()(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box,
                                     elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -1048,9 +1010,14 @@ struct TcGemm {
   int* d_counters = nullptr;
   int* d_status = nullptr;
   int* d_cut = nullptr;
+  // Tensor maps of recent operand pointers (the shape is fixed per handle): a serving loop alternates among
+  // a few activation buffers and one weight pointer, so the driver call is paid once per pointer.
+  struct CachedMap { const void* ptr = nullptr; CUtensorMap map; };
+  CachedMap act_maps[4], high_map;
+  int act_next = 0;
 };
 
-static void validate(const hg_problem& l, const hg_problem& h, bool fused = false) {
+void validate(const hg_problem& l, const hg_problem& h, bool fused) {
   const hg_problem& any = l.rows ? l : h;
   if (l.rows < 0 || h.rows < 0 || l.rows + h.rows == 0) throw std::runtime_error("Hybrid GEMM needs at least one weight row");
   if (any.tokens <= 0 || any.k <= 0 || any.k % 128 || any.outputs <= 0) throw std::runtime_error("Invalid hybrid GEMM shape");
@@ -1130,8 +1097,27 @@ static void launch_reduce(const Plan& plan, const TcParams& p, const int* cut_ti
   }
 }
 
+// Everything of the kernel parameters that follows from the problems and the plan; the caller adds the
+// output target, the fused activations and the schedule / scratch pointers.
+static TcParams base_params(const Plan& plan, const hg_problem& l, const hg_problem& h, int dtype) {
+  const hg_problem& any = l.rows ? l : h;
+  TcParams p{};
+  p.rows[0] = l.rows; p.rows[1] = h.rows;
+  p.tiles[0] = (l.rows + kTileRows - 1) / kTileRows; p.tiles[1] = (h.rows + kTileRows - 1) / kTileRows;
+  p.sfa[0] = static_cast<const uint8_t*>(l.weight_scales); p.sfa[1] = static_cast<const uint8_t*>(h.weight_scales);
+  p.ids[0] = static_cast<const int32_t*>(l.ids); p.ids[1] = static_cast<const int32_t*>(h.ids);
+  p.sfb = static_cast<const uint8_t*>(any.activation_scales);
+  p.outputs = any.outputs; p.tokens = any.tokens; p.k = any.k; p.kblocks = any.k / kTileK;
+  p.n_tile = plan.n_tile; p.stages = plan.stages; p.dtype = dtype; p.tmem_cols = uint32_t(plan.tmem_cols);
+  p.issuers = plan.issuers;
+  p.acc_slots = plan.acc_slots;
+  p.external_reduce = plan.external_reduce ? 1 : 0;
+  p.weight_low = static_cast<const uint8_t*>(l.weight);
+  return p;
+}
+
 void tc_run(TcGemm* g, const hg_problem& l, const hg_problem& h, cudaStream_t stream, const void* x, int x_dtype,
-            const PeerPush* push) {
+            const PartialTarget* partial) {
   const bool fused = x != nullptr;
   validate(l, h, fused);
   if (fused) {
@@ -1143,56 +1129,57 @@ void tc_run(TcGemm* g, const hg_problem& l, const hg_problem& h, cudaStream_t st
   if (l.rows != g->rows[0] || h.rows != g->rows[1] || any.tokens != g->tokens || any.k != g->k || any.outputs != g->outputs)
     throw std::runtime_error("Hybrid GEMM handle was created for a different shape");
   const Plan& plan = g->plan;
-  TcParams p{};
-  p.rows[0] = l.rows; p.rows[1] = h.rows;
-  p.tiles[0] = (l.rows + kTileRows - 1) / kTileRows; p.tiles[1] = (h.rows + kTileRows - 1) / kTileRows;
-  p.sfa[0] = static_cast<const uint8_t*>(l.weight_scales); p.sfa[1] = static_cast<const uint8_t*>(h.weight_scales);
-  p.ids[0] = static_cast<const int32_t*>(l.ids); p.ids[1] = static_cast<const int32_t*>(h.ids);
-  p.sfb = static_cast<const uint8_t*>(any.activation_scales);
-  if (push) {
-    // Slot `rank` of every rank's receive buffer; the own buffer first so a one-rank world behaves like hg_run.
-    if (push->world < 1 || push->world > HG_TP_MAX_WORLD || push->rank < 0 || push->rank >= push->world)
-      throw std::runtime_error("Tensor-parallel world must be 1..8 with rank inside it");
-    if (!push->recv || !push->state) throw std::runtime_error("Null receive buffers or state");
-    if (push->slot_elems < int64_t(any.tokens) * any.outputs) throw std::runtime_error("Receive slot smaller than tokens x outputs");
-    for (int i = 0; i < push->world; ++i) {
-      const int w = (push->rank + i) % push->world;
-      if (!push->recv[w] || (reinterpret_cast<uintptr_t>(push->recv[w]) & 15)) throw std::runtime_error("Receive buffers must be 16-byte aligned");
-      p.out.ptr[i] = static_cast<uint16_t*>(push->recv[w]) + int64_t(push->rank) * push->slot_elems;
-    }
-    p.out.count = push->world;
-    p.out.epoch = push->state;
-    p.out.parity_stride = int64_t(push->world) * push->slot_elems;
+  TcParams p = base_params(plan, l, h, g->dtype);
+  if (partial) {
+    // This rank's exchange buffer (two halves); decode sizes travel as fp32 so the sum is rounded once.
+    if (!partial->buffer || !partial->state) throw std::runtime_error("Null exchange buffer or state");
+    if (reinterpret_cast<uintptr_t>(partial->buffer) & 15 || partial->half_bytes % 16) throw std::runtime_error("Exchange buffer halves must be 16-byte aligned");
+    if (partial->half_bytes < int64_t(any.tokens) * any.outputs * (partial->f32 ? 4 : 2))
+      throw std::runtime_error("Exchange buffer half smaller than tokens x outputs");
+    p.out.ptr = partial->buffer;
+    p.out.f32 = partial->f32 ? 1 : 0;
+    p.out.epoch = partial->state;
+    p.out.parity_bytes = partial->half_bytes;
   } else {
-    p.out.ptr[0] = static_cast<uint16_t*>(any.output);
-    p.out.count = 1;
+    p.out.ptr = any.output;
   }
-  p.outputs = any.outputs; p.tokens = any.tokens; p.k = any.k; p.kblocks = any.k / kTileK;
-  p.n_tile = plan.n_tile; p.stages = plan.stages; p.dtype = g->dtype; p.tmem_cols = uint32_t(plan.tmem_cols);
-  p.issuers = plan.issuers;
-  p.acc_slots = plan.acc_slots;
-  p.external_reduce = plan.external_reduce ? 1 : 0;
-  p.weight_low = static_cast<const uint8_t*>(l.weight);
-  p.prefetch_stages = prefetch_stages();
   p.x = static_cast<const uint16_t*>(x);
   p.x_bf16 = x_dtype == HG_DTYPE_BF16;
   p.units = g->d_units; p.cta_begin = g->d_cta_begin;
   p.workspace = g->d_workspace; p.counters = g->d_counters; p.status = g->d_status;
-  // An absent high partition (or, in fused mode, the activation map) still needs a valid descriptor; it is
-  // never dereferenced.
-  const CUtensorMap map_act = make_map(fused ? x : any.activation, any.tokens, any.k, plan.n_tile);
-  const CUtensorMap map_high = h.rows ? make_map(h.weight, h.rows, h.k, kTileRows) : map_act;
-  // Packed MXFP4 rows as bytes: one 128-byte x 128-row box is a K256 stage (used for L2 prefetch only).
-  const CUtensorMap map_low = l.rows ? make_map(l.weight, l.rows, l.k / 2, kTileRows, std::min(128, l.k / 2)) : map_act;
+  // Tensor maps by operand pointer.  A map that the launch does not use (no MXFP8 rows; activations
+  // quantised in the kernel) is passed as zeros and never touched by the kernel.
+  static const CUtensorMap no_map{};
+  const CUtensorMap* map_act = &no_map;
+  if (!fused) {
+    TcGemm::CachedMap* hit = nullptr;
+    for (auto& entry : g->act_maps)
+      if (entry.ptr == any.activation) hit = &entry;
+    if (!hit) {
+      hit = &g->act_maps[g->act_next];
+      g->act_next = (g->act_next + 1) % 4;
+      hit->map = make_map(any.activation, any.tokens, any.k, plan.n_tile);
+      hit->ptr = any.activation;
+    }
+    map_act = &hit->map;
+  }
+  const CUtensorMap* map_high = &no_map;
+  if (h.rows) {
+    if (g->high_map.ptr != h.weight) {
+      g->high_map.map = make_map(h.weight, h.rows, h.k, kTileRows);
+      g->high_map.ptr = h.weight;
+    }
+    map_high = &g->high_map.map;
+  }
   const dim3 grid(plan.grid), plain(kTcThreads - kQuantThreads), with_quantisers(kTcThreads);
   const bool bf16 = g->dtype == HG_DTYPE_BF16;
   cudaError_t launched;
   if (fused)
-    launched = bf16 ? launch_kernel(hybrid_gemm_tc_kernel<__nv_bfloat16, true>, grid, with_quantisers, plan.smem_bytes, stream, p, map_high, map_act, map_low, g->heads)
-                    : launch_kernel(hybrid_gemm_tc_kernel<__half, true>, grid, with_quantisers, plan.smem_bytes, stream, p, map_high, map_act, map_low, g->heads);
+    launched = bf16 ? launch_kernel(hybrid_gemm_tc_kernel<__nv_bfloat16, true>, grid, with_quantisers, plan.smem_bytes, stream, p, *map_high, *map_act, g->heads)
+                    : launch_kernel(hybrid_gemm_tc_kernel<__half, true>, grid, with_quantisers, plan.smem_bytes, stream, p, *map_high, *map_act, g->heads);
   else
-    launched = bf16 ? launch_kernel(hybrid_gemm_tc_kernel<__nv_bfloat16, false>, grid, plain, plan.smem_bytes, stream, p, map_high, map_act, map_low, g->heads)
-                    : launch_kernel(hybrid_gemm_tc_kernel<__half, false>, grid, plain, plan.smem_bytes, stream, p, map_high, map_act, map_low, g->heads);
+    launched = bf16 ? launch_kernel(hybrid_gemm_tc_kernel<__nv_bfloat16, false>, grid, plain, plan.smem_bytes, stream, p, *map_high, *map_act, g->heads)
+                    : launch_kernel(hybrid_gemm_tc_kernel<__half, false>, grid, plain, plan.smem_bytes, stream, p, *map_high, *map_act, g->heads);
   check(launched, "hybrid GEMM launch");
   launch_reduce(plan, p, g->d_cut, g->dtype, stream, true);
 }
@@ -1234,24 +1221,37 @@ void tc_status(TcGemm* g, cudaStream_t stream, int out[3]) {
 // * The array is HG_STATIC_SCRATCH_BYTES long on every GPU that loads the library, until exit.
 // * `g_static_scratch` is a device symbol.  Host code cannot use its name as a pointer; the device
 //   address is looked up once per device with cudaGetSymbolAddress, with that device current.  That
-//   look-up (and raising the kernel's shared-memory limit) happens in the first call on a device, so
-//   make that first call before any stream capture.
+//   look-up (and raising the kernel's shared-memory limit) happens in the first call on a device.
+// * The call is NOT for stream capture: it copies the schedule of the shape from host memory into the
+//   array whenever the array holds another shape's schedule, and a captured copy would replay from
+//   host memory that a later call rewrites.  A capturing stream is refused with an error.
 // * All calls share the array: two calls that overlap on the GPU (different streams) race on it.
 //   Calls on one stream are ordered and safe.  Counters and status words are cleared at the start
-//   of every call, whatever an earlier call left behind.
+//   of every call, whatever an earlier call left behind; hg_static_status reads the status words of
+//   the calls since its last read.
 // * A shape whose schedule and partial sums do not fit is rejected with an error; nothing is launched.
 
 static __device__ __align__(256) unsigned char g_static_scratch[HG_STATIC_SCRATCH_BYTES];
 
 namespace {
 
+constexpr int kStaticPlans = 8;   // schedules kept on the host, least recently used replaced
+
+struct StaticPlan {
+  int key[6] = {0, 0, 0, 0, 0, 0};
+  uint64_t used = 0;             // 0 = empty
+  Plan plan;
+  CtaHeads heads{};
+};
+
 struct StaticState {
   std::mutex mutex;
   unsigned char* base[64] = {};   // device address of g_static_scratch, per device ordinal
   int sms[64] = {};
-  bool have_plan = false;         // last schedule, reused while the shape repeats
-  int key[6] = {0, 0, 0, 0, 0, 0};
-  Plan plan;
+  const StaticPlan* resident[64] = {};   // whose schedule the array of that device holds
+  uint64_t resident_stamp[64] = {};
+  StaticPlan plans[kStaticPlans];
+  uint64_t clock = 0;
 };
 
 StaticState& static_state() {
@@ -1261,17 +1261,11 @@ StaticState& static_state() {
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-}  // namespace
+// Where the three status words of the static path live: they are accumulated over calls (the kernel
+// only ever adds to [1] and [2] and sets [0] once), so they sit apart from what each call clears.
+constexpr size_t kStaticStatusOffset = 0, kStaticCountersOffset = 256;
 
-void tc_run_static(int schedule, const hg_problem& l, const hg_problem& h, int dtype, cudaStream_t stream) {
-  validate(l, h);
-  if (dtype != HG_DTYPE_F16 && dtype != HG_DTYPE_BF16) throw std::runtime_error("Unknown output dtype");
-  if (schedule < HG_SCHEDULE_AUTO || schedule > HG_SCHEDULE_STREAM_K) throw std::runtime_error("Unknown tile schedule id");
-  const hg_problem& any = l.rows ? l : h;
-  StaticState& st = static_state();
-  std::lock_guard<std::mutex> lock(st.mutex);
-  int device = 0;
-  check(cudaGetDevice(&device), "cudaGetDevice");
+unsigned char* static_base(StaticState& st, int device) {
   if (device < 0 || device >= 64) throw std::runtime_error("hg_run_static supports device ordinals 0..63");
   if (!st.base[device]) {
     // Once per device, with that device current: device address of the symbol, SM count, kernel limits.
@@ -1282,18 +1276,46 @@ void tc_run_static(int schedule, const hg_problem& l, const hg_problem& h, int d
     configure_kernel<__half>();
     st.base[device] = static_cast<unsigned char*>(address);
   }
+  return st.base[device];
+}
+
+}  // namespace
+
+void tc_run_static(int schedule, const hg_problem& l, const hg_problem& h, int dtype, cudaStream_t stream) {
+  validate(l, h);
+  if (dtype != HG_DTYPE_F16 && dtype != HG_DTYPE_BF16) throw std::runtime_error("Unknown output dtype");
+  if (schedule < HG_SCHEDULE_AUTO || schedule > HG_SCHEDULE_STREAM_K) throw std::runtime_error("Unknown tile schedule id");
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  check(cudaStreamIsCapturing(stream, &capturing), "cudaStreamIsCapturing");
+  if (capturing != cudaStreamCaptureStatusNone)
+    throw std::runtime_error("hg_run_static cannot be captured into a CUDA graph (it copies a schedule from host memory); "
+                             "use hg_create/hg_run under capture");
+  const hg_problem& any = l.rows ? l : h;
+  StaticState& st = static_state();
+  std::lock_guard<std::mutex> lock(st.mutex);
+  int device = 0;
+  check(cudaGetDevice(&device), "cudaGetDevice");
+  unsigned char* base = static_base(st, device);
   const int key[6] = {l.rows, h.rows, any.tokens, any.k, schedule, st.sms[device]};
-  if (!st.have_plan || std::memcmp(key, st.key, sizeof(key)) != 0) {
-    st.plan = make_plan(l.rows, h.rows, any.tokens, any.k, st.sms[device], schedule);
-    std::memcpy(st.key, key, sizeof(key));
-    st.have_plan = true;
+  StaticPlan* entry = nullptr;
+  StaticPlan* oldest = &st.plans[0];
+  for (StaticPlan& candidate : st.plans) {
+    if (candidate.used && std::memcmp(key, candidate.key, sizeof(key)) == 0) entry = &candidate;
+    if (candidate.used < oldest->used) oldest = &candidate;
   }
-  const Plan& plan = st.plan;
+  if (!entry) {
+    entry = oldest;
+    for (auto& resident : st.resident)
+      if (resident == entry) resident = nullptr;   // the array of that device holds a schedule that is going away
+    entry->plan = make_plan(l.rows, h.rows, any.tokens, any.k, st.sms[device], schedule);
+    entry->heads = make_heads(entry->plan);
+    std::memcpy(entry->key, key, sizeof(key));
+  }
+  entry->used = ++st.clock;
+  const Plan& plan = entry->plan;
 
   // Carve the array: status | counters | cta_begin | units | cut list | workspace.
-  const size_t off_status = 0;
-  const size_t off_counters = 256;
-  const size_t off_cta = align_up(off_counters + sizeof(int) * size_t(std::max(1, plan.counters)), 256);
+  const size_t off_cta = align_up(kStaticCountersOffset + sizeof(int) * size_t(std::max(1, plan.counters)), 256);
   const size_t off_units = align_up(off_cta + sizeof(int) * plan.cta_begin.size(), 256);
   const size_t off_cut = align_up(off_units + sizeof(WorkUnit) * std::max<size_t>(1, plan.units.size()), 256);
   const size_t off_work = align_up(off_cut + sizeof(int) * std::max<size_t>(4, plan.cut_tiles.size()), 256);
@@ -1302,45 +1324,51 @@ void tc_run_static(int schedule, const hg_problem& l, const hg_problem& h, int d
     throw std::runtime_error("hg_run_static: this shape needs " + std::to_string(total) +
                              " bytes of scratch (schedule and split-K partial sums) but the static buffer holds " +
                              std::to_string(size_t(HG_STATIC_SCRATCH_BYTES)) + "; use hg_create/hg_run");
-  unsigned char* base = st.base[device];
-  check(cudaMemsetAsync(base, 0, off_cta, stream), "clear static status and counters");
-  check(cudaMemcpyAsync(base + off_cta, plan.cta_begin.data(), sizeof(int) * plan.cta_begin.size(),
-                        cudaMemcpyHostToDevice, stream), "upload schedule");
-  check(cudaMemcpyAsync(base + off_units, plan.units.data(), sizeof(WorkUnit) * plan.units.size(),
-                        cudaMemcpyHostToDevice, stream), "upload units");
-  if (!plan.cut_tiles.empty())
-    check(cudaMemcpyAsync(base + off_cut, plan.cut_tiles.data(), sizeof(int) * plan.cut_tiles.size(),
-                          cudaMemcpyHostToDevice, stream), "upload cut list");
+  // Arrival counters start every call at zero; the status words are only cleared by hg_static_status.
+  check(cudaMemsetAsync(base + kStaticCountersOffset, 0, off_cta - kStaticCountersOffset, stream), "clear static counters");
+  if (st.resident[device] != entry) {
+    // The schedule of another shape (or nothing) is in the array: copy this one in.  The vectors stay
+    // alive in their cache entry; an entry is only rebuilt under the mutex, after which it is copied again.
+    check(cudaMemcpyAsync(base + off_cta, plan.cta_begin.data(), sizeof(int) * plan.cta_begin.size(),
+                          cudaMemcpyHostToDevice, stream), "upload schedule");
+    check(cudaMemcpyAsync(base + off_units, plan.units.data(), sizeof(WorkUnit) * plan.units.size(),
+                          cudaMemcpyHostToDevice, stream), "upload units");
+    if (!plan.cut_tiles.empty())
+      check(cudaMemcpyAsync(base + off_cut, plan.cut_tiles.data(), sizeof(int) * plan.cut_tiles.size(),
+                            cudaMemcpyHostToDevice, stream), "upload cut list");
+    st.resident[device] = entry;
+  }
 
-  TcParams p{};
-  p.rows[0] = l.rows; p.rows[1] = h.rows;
-  p.tiles[0] = (l.rows + kTileRows - 1) / kTileRows; p.tiles[1] = (h.rows + kTileRows - 1) / kTileRows;
-  p.sfa[0] = static_cast<const uint8_t*>(l.weight_scales); p.sfa[1] = static_cast<const uint8_t*>(h.weight_scales);
-  p.ids[0] = static_cast<const int32_t*>(l.ids); p.ids[1] = static_cast<const int32_t*>(h.ids);
-  p.sfb = static_cast<const uint8_t*>(any.activation_scales);
-  p.out.ptr[0] = static_cast<uint16_t*>(any.output);
-  p.out.count = 1;
-  p.outputs = any.outputs; p.tokens = any.tokens; p.k = any.k; p.kblocks = any.k / kTileK;
-  p.n_tile = plan.n_tile; p.stages = plan.stages; p.dtype = dtype; p.tmem_cols = uint32_t(plan.tmem_cols);
-  p.issuers = plan.issuers;
-  p.acc_slots = plan.acc_slots;
-  p.external_reduce = plan.external_reduce ? 1 : 0;
-  p.weight_low = static_cast<const uint8_t*>(l.weight);
-  p.status = reinterpret_cast<int*>(base + off_status);
-  p.counters = reinterpret_cast<int*>(base + off_counters);
+  TcParams p = base_params(plan, l, h, dtype);
+  p.out.ptr = any.output;
+  p.status = reinterpret_cast<int*>(base + kStaticStatusOffset);
+  p.counters = reinterpret_cast<int*>(base + kStaticCountersOffset);
   p.cta_begin = reinterpret_cast<const int*>(base + off_cta);
   p.units = reinterpret_cast<const WorkUnit*>(base + off_units);
   p.workspace = reinterpret_cast<float*>(base + off_work);
+  static const CUtensorMap no_map{};
   const CUtensorMap map_act = make_map(any.activation, any.tokens, any.k, plan.n_tile);
-  const CUtensorMap map_high = h.rows ? make_map(h.weight, h.rows, h.k, kTileRows) : map_act;
-  // Packed MXFP4 rows as bytes: one 128-byte x 128-row box is a K256 stage (used for L2 prefetch only).
-  const CUtensorMap map_low = l.rows ? make_map(l.weight, l.rows, l.k / 2, kTileRows, std::min(128, l.k / 2)) : map_act;
+  const CUtensorMap map_high = h.rows ? make_map(h.weight, h.rows, h.k, kTileRows) : no_map;
+  // Plain launches (no programmatic overlap): the clears and copies above are ordered before the kernel.
   if (dtype == HG_DTYPE_BF16)
-    hybrid_gemm_tc_kernel<__nv_bfloat16, false><<<plan.grid, kTcThreads - kQuantThreads, plan.smem_bytes, stream>>>(p, map_high, map_act, map_low, make_heads(plan));
+    hybrid_gemm_tc_kernel<__nv_bfloat16, false><<<plan.grid, kTcThreads - kQuantThreads, plan.smem_bytes, stream>>>(p, map_high, map_act, entry->heads);
   else
-    hybrid_gemm_tc_kernel<__half, false><<<plan.grid, kTcThreads - kQuantThreads, plan.smem_bytes, stream>>>(p, map_high, map_act, map_low, make_heads(plan));
+    hybrid_gemm_tc_kernel<__half, false><<<plan.grid, kTcThreads - kQuantThreads, plan.smem_bytes, stream>>>(p, map_high, map_act, entry->heads);
   check(cudaGetLastError(), "hybrid GEMM launch (static scratch)");
   launch_reduce(plan, p, reinterpret_cast<const int*>(base + off_cut), dtype, stream, false);
+}
+
+void tc_static_status(cudaStream_t stream, int out[3]) {
+  StaticState& st = static_state();
+  std::lock_guard<std::mutex> lock(st.mutex);
+  int device = 0;
+  check(cudaGetDevice(&device), "cudaGetDevice");
+  unsigned char* base = static_base(st, device);
+  int host[3] = {0, 0, 0};
+  check(cudaMemcpyAsync(host, base + kStaticStatusOffset, sizeof(host), cudaMemcpyDeviceToHost, stream), "status read");
+  check(cudaMemsetAsync(base + kStaticStatusOffset, 0, sizeof(host), stream), "status clear");
+  check(cudaStreamSynchronize(stream), "status sync");
+  out[0] = host[0]; out[1] = host[1]; out[2] = host[2];
 }
 
 }  // namespace hg
@@ -1349,5 +1377,12 @@ extern "C" int hg_run_static(int schedule, const hg_problem* low, const hg_probl
   HG_TRY
   if (!low || !high) throw std::runtime_error("Null argument to hg_run_static");
   hg::tc_run_static(schedule, *low, *high, dtype, static_cast<cudaStream_t>(stream));
+  HG_CATCH
+}
+
+extern "C" int hg_static_status(void* stream, int* status) {
+  HG_TRY
+  if (!status) throw std::runtime_error("Null argument to hg_static_status");
+  hg::tc_static_status(static_cast<cudaStream_t>(stream), status);
   HG_CATCH
 }

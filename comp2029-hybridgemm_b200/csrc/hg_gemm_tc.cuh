@@ -48,22 +48,28 @@ struct TcGemm;  // opaque device-side state (plan buffers, workspace, counters, 
 TcGemm* tc_create(const hg_problem& l, const hg_problem& h, int schedule, int dtype, cudaStream_t stream);
 // `x` (optional): 16-bit activations [tokens,k] to quantise inside the GEMM kernel (at most 16 tokens);
 // the problems' activation / activation_scales pointers are then ignored.
-// `push` (optional): row-parallel tensor parallelism; the epilogue stores the partial result into slot
-// `rank` of every rank's receive buffer (see hg_run_push) instead of the problems' `output`.
-struct PeerPush {
-  void* const* recv;   // world base pointers, as mapped on this GPU
-  int world, rank;
-  int64_t slot_elems;  // 16-bit elements per rank slot
+// `partial` (optional): row-parallel tensor parallelism; the result goes to this rank's half of a peer-mapped
+// exchange buffer (see hg_run_partial) instead of the problems' `output`.
+struct PartialTarget {
+  void* buffer;        // this rank's exchange buffer: two halves of half_bytes
+  int64_t half_bytes;
+  int f32;             // store fp32 partial sums instead of 16-bit ones
   const int* state;    // device word counting finished exchanges
 };
 void tc_run(TcGemm*, const hg_problem& l, const hg_problem& h, cudaStream_t stream, const void* x = nullptr,
-            int x_dtype = HG_DTYPE_BF16, const PeerPush* push = nullptr);
+            int x_dtype = HG_DTYPE_BF16, const PartialTarget* partial = nullptr);
 void tc_destroy(TcGemm*);
 const Plan& tc_plan(const TcGemm*);
 void tc_kernel_attributes(int* registers, int* local_bytes);
 // Reads (and clears) the device status words: [0] error code of a bounded wait
 // that gave up, [1] K128 blocks issued to the tensor core, [2] work units stored.
 void tc_status(TcGemm*, cudaStream_t stream, int out[3]);
+// Same three words for the launches of hg_run_static on the current device since the last read.
+void tc_static_status(cudaStream_t stream, int out[3]);
+// Argument rule shared by every GEMM path (tensor-core and SIMT): shapes, shared operands, null and
+// misaligned pointers throw.  `fused`: activations are quantised in the kernel, the problems' activation
+// pointers are ignored.
+void validate(const hg_problem& l, const hg_problem& h, bool fused = false);
 
 void run_simt_pair(const hg_problem& l, const hg_problem& h, cudaStream_t stream, int tokens_per_pass, int dtype);
 

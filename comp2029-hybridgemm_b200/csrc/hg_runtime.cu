@@ -15,6 +15,8 @@ static bool same_shape(const hg_problem& a, const hg_problem& b) {
 // Counterpart of the reference's Runner (runtime.cu:20-44).  The reference owns
 // two kernels, a side stream and fork/join events; here one persistent launch
 // covers both partitions, so the stream policies 0-3 all enqueue that launch.
+constexpr int kReferenceVariants = 45, kLastSimtVariant = 34;
+
 struct Runner {
   hg_problem low{}, high{};
   int low_id = 0, high_id = 0, dtype = HG_DTYPE_F16;
@@ -26,17 +28,26 @@ struct Runner {
     if (l.rows == 0 && h.rows == 0) throw std::runtime_error("Hybrid GEMM needs at least one weight row");
     // The partitions share one launch: the low partition's id decides unless it is absent or AUTO.
     int schedule = l.rows && li ? li : (h.rows && hi ? hi : (li ? li : hi));
-    if (schedule == HG_SCHEDULE_SIMT) schedule = HG_SCHEDULE_AUTO;   // tensor-core handle still serves policies 0-3
-    if (schedule > HG_SCHEDULE_STREAM_K) throw std::runtime_error("Unknown schedule id " + std::to_string(schedule));
+    // Ids above the three schedules of this library are the reference's variant ids (45 of them,
+    // src/kernel/output_channel_gemm.h:41): 28-34, its SIMT family, select the SIMT kernel here; the rest name
+    // CUTLASS and cp.async tile shapes that have no counterpart, so a plan tuned on the reference's GPU still
+    // loads and runs with the schedule chosen from the shape.  The tensor-core handle always exists: it serves
+    // policies 0-3 whatever the id.
+    if (schedule >= kReferenceVariants) throw std::runtime_error("Unknown schedule id " + std::to_string(schedule));
+    if (schedule > HG_SCHEDULE_STREAM_K) schedule = HG_SCHEDULE_AUTO;
     tc = tc_create(l, h, schedule, dt, s);
   }
   ~Runner() { tc_destroy(tc); }
 
-  bool simt_only() const { return (low.rows ? low_id : high_id) == HG_SCHEDULE_SIMT; }
+  bool simt_only() const {
+    const int id = low.rows ? low_id : high_id;
+    return id >= HG_SCHEDULE_SIMT && id <= kLastSimtVariant;
+  }
 
   void run(const hg_problem& l, const hg_problem& h, cudaStream_t s, int policy) {
     if (!same_shape(l, low) || !same_shape(h, high)) throw std::runtime_error("Kernel cannot rebind to a different shape");
     if (policy < 0 || policy > HG_POLICY_GEMV_PAIR4) throw std::runtime_error("Unknown launch policy");
+    validate(l, h);   // every path, the SIMT kernel included: a bad pointer is an error, never a launch
     if (policy >= HG_POLICY_GEMV_PAIR1) run_simt_pair(l, h, s, 1 << (policy - HG_POLICY_GEMV_PAIR1), dtype);
     else if (simt_only()) run_simt_pair(l, h, s, 4, dtype);
     else tc_run(tc, l, h, s);
@@ -49,10 +60,10 @@ struct Runner {
     tc_run(tc, l, h, s, x, x_dtype);
   }
 
-  // Row-parallel tensor parallelism: partial results go to every rank's receive buffer (see hg_run_push).
-  void run_push(const hg_problem& l, const hg_problem& h, const void* x, int x_dtype, const PeerPush& push, cudaStream_t s) {
+  // Row-parallel tensor parallelism: the partial result goes to this rank's exchange buffer (see hg_run_partial).
+  void run_partial(const hg_problem& l, const hg_problem& h, const void* x, int x_dtype, const PartialTarget& target, cudaStream_t s) {
     if (!same_shape(l, low) || !same_shape(h, high)) throw std::runtime_error("Kernel cannot rebind to a different shape");
-    tc_run(tc, l, h, s, x, x_dtype, &push);
+    tc_run(tc, l, h, s, x, x_dtype, &target);
   }
 };
 
@@ -97,12 +108,12 @@ int hg_run_x(void* handle, const hg_problem* l, const hg_problem* h, const void*
   HG_CATCH
 }
 
-int hg_run_push(void* handle, const hg_problem* l, const hg_problem* h, const void* x, int x_dtype,
-                void* const* recv, int world, int rank, int64_t slot_elems, const int* state, void* stream) {
+int hg_run_partial(void* handle, const hg_problem* l, const hg_problem* h, const void* x, int x_dtype,
+                   void* buffer, int64_t half_bytes, int f32, const int* state, void* stream) {
   HG_TRY
-  if (!handle || !l || !h) throw std::runtime_error("Null argument to hg_run_push");
-  const hg::PeerPush push{recv, world, rank, slot_elems, state};
-  static_cast<hg::Runner*>(handle)->run_push(*l, *h, x, x_dtype, push, static_cast<cudaStream_t>(stream));
+  if (!handle || !l || !h) throw std::runtime_error("Null argument to hg_run_partial");
+  const hg::PartialTarget target{buffer, half_bytes, f32, state};
+  static_cast<hg::Runner*>(handle)->run_partial(*l, *h, x, x_dtype, target, static_cast<cudaStream_t>(stream));
   HG_CATCH
 }
 

@@ -35,6 +35,8 @@ FUSED_QUANT_TOKENS = 16 if os.environ.get("HYGEMM_FUSED_QUANT", "1") != "0" else
 # many output channels keep the separate quantiser launch (gate_up, 37888 wide, measured 30.8 us with its own
 # quantiser launch against 36.3 us fused at 16 tokens; the narrow layers gain from the missing launch).
 FUSED_QUANT_MAX_OUTPUTS = int(os.environ.get("HYGEMM_FUSED_QUANT_MAX_OUTPUTS", "8192"))
+# Row-parallel exchange: up to this many tokens the partial sums cross NVLink as fp32 (rounded once after the sum).
+FUSED_QUANT_TOKENS_F32 = 16
 # Launch policies of hg_run (reference: native.py:14-15).
 POLICIES = {"serial": 0, "concurrent": 1, "high_first": 2, "high_main": 3,
             "gemv_pair1": 4, "gemv_pair2": 5, "gemv_pair4": 6}
@@ -77,8 +79,9 @@ def library():
     lib.hg_destroy.argtypes, lib.hg_destroy.restype = [vp], None
     lib.hg_plan.argtypes = [ci] * 6 + [C.POINTER(ci), C.POINTER(ci), ci]
     lib.hg_run_static.argtypes = [ci, pp, pp, vp, ci]
-    lib.hg_run_push.argtypes = [vp, pp, pp, vp, ci, C.POINTER(vp), ci, ci, C.c_int64, vp, vp]
-    lib.hg_tp_reduce.argtypes = [vp, vp, C.c_int64, C.c_int64, ci, ci, C.POINTER(vp), vp, ci, vp]
+    lib.hg_static_status.argtypes = [vp, C.POINTER(ci)]
+    lib.hg_run_partial.argtypes = [vp, pp, pp, vp, ci, vp, C.c_int64, ci, vp, vp]
+    lib.hg_tp_allreduce.argtypes = [C.POINTER(vp), vp, C.c_int64, C.c_int64, ci, ci, ci, C.POINTER(vp), vp, ci, vp]
     lib.hg_tp_status.argtypes = [vp, vp, C.POINTER(ci)]
     lib.hg_fused_error.restype = C.c_char_p
     lib.hg_fused_create.argtypes = [ci, pp, pp, vp, C.POINTER(vp)]
@@ -153,6 +156,9 @@ class DualLinear:
         self.lo = rows[~selected].to(torch.int32)
         self.w4, self.sf4 = pack(weight.index_select(0, self.lo.long()).contiguous(), True)
         self.w8, self.sf8 = pack(weight.index_select(0, self.hi.long()).contiguous(), False)
+        # The GEMM starts reading weights before it waits for the kernel in front of it (programmatic
+        # dependent launch), so the packed weights must be complete before the first call: load time only.
+        torch.cuda.current_stream(weight.device).synchronize()
         self.low_id, self.high_id, self.concurrent = low_id, high_id, concurrent
         self.handles = {}
         self.fused_handles = {}
@@ -165,7 +171,7 @@ class DualLinear:
         if x.ndim != 2 or x.shape[1] != self.k or x.device != self.w4.device:
             raise ValueError("HyGEMM input shape/device does not match its weights")
         if 0 < x.shape[0] <= FUSED_QUANT_TOKENS and x.dtype in DTYPES and x.is_contiguous() and not self.plans \
-                and self.low_id != 28 and self.outputs <= FUSED_QUANT_MAX_OUTPUTS:
+                and not 28 <= self.low_id <= 34 and self.outputs <= FUSED_QUANT_MAX_OUTPUTS:
             return self._run_fused(x)
         q, sf = pack(x)
         return self.run_packed(q, sf)
@@ -246,11 +252,13 @@ class DualLinear:
         return y
 
     def run_exchange(self, exchange, x=None, q=None, sf=None):
-        """Row-parallel shard: the GEMM pushes its partial sums into every rank's receive buffer from its
-        epilogue and a second launch waits for all ranks and adds them (`hg_run_push` + `hg_tp_reduce`).
+        """Row-parallel shard: the GEMM writes its partial sums into this rank's peer-mapped exchange buffer and
+        a second launch waits for all ranks, pulls their partials over NVLink and adds them in rank order
+        (`hg_run_partial` + `hg_tp_allreduce`).
 
-        `exchange` is a `tp.PeerExchange`.  Pass 16-bit `x` (at most FUSED_QUANT_TOKENS tokens, quantised in
-        the GEMM launch) or prepacked `(q, sf)`.  Returns the summed `[tokens, outputs]`, identical on every rank.
+        `exchange` is a `tp.PeerExchange`.  Pass 16-bit `x` (at most FUSED_QUANT_TOKENS tokens, quantised in the
+        GEMM launch) or prepacked `(q, sf)`.  Returns the summed `[tokens, outputs]`, identical on every rank;
+        a peer that never arrives turns it into NaN and leaves a status behind (`exchange.status()`).
         """
         fused = x is not None
         src = x if fused else q
@@ -261,19 +269,21 @@ class DualLinear:
             raise ValueError("Fused quantisation serves at most 16 tokens of FP16/BF16")
         if not fused and (sf is None or sf.numel() != scale_size(tokens, self.k)):
             raise ValueError("Invalid prepacked MXFP8 scale buffer")
-        if tokens * self.outputs > exchange.slot_elems or self.dtype != exchange.dtype:
+        elems = tokens * self.outputs
+        if elems * 2 > exchange.half_bytes or self.dtype != exchange.dtype or elems % 8:
             raise ValueError("Exchange buffers are too small or of another dtype")
+        # Decode sizes exchange fp32 partial sums, so the result is rounded once instead of once per rank.
+        f32 = int(tokens <= FUSED_QUANT_TOKENS_F32 and elems * 4 <= exchange.half_bytes)
         y = torch.empty((tokens, self.outputs), dtype=self.dtype, device=src.device)
         low, high, _, low_ref, high_ref = self._rebound(tokens, src, src if fused else sf, y)
         stream = _stream(src.device)
         handle = self._handle(tokens, self.low_id, self.high_id, low_ref, high_ref, stream)
         lib = library()
-        check(lib.hg_run_push(handle, low_ref, high_ref, x.data_ptr() if fused else None,
-                              DTYPES[x.dtype] if fused else 0, exchange.recv_ptrs, exchange.world, exchange.rank,
-                              exchange.slot_elems, exchange.state.data_ptr(), stream))
-        check(lib.hg_tp_reduce(exchange.recv.data_ptr(), y.data_ptr(), tokens * self.outputs, exchange.slot_elems,
-                               exchange.world, exchange.rank, exchange.flag_ptrs, exchange.state.data_ptr(),
-                               DTYPES[self.dtype], stream))
+        check(lib.hg_run_partial(handle, low_ref, high_ref, x.data_ptr() if fused else None,
+                                 DTYPES[x.dtype] if fused else 0, exchange.buffer.data_ptr(), exchange.half_bytes, f32,
+                                 exchange.state.data_ptr(), stream))
+        check(lib.hg_tp_allreduce(exchange.buffer_ptrs, y.data_ptr(), elems, exchange.half_bytes, f32, exchange.world,
+                                  exchange.rank, exchange.flag_ptrs, exchange.state.data_ptr(), DTYPES[self.dtype], stream))
         self.calls[tokens] = self.calls.get(tokens, 0) + 1
         return y
 

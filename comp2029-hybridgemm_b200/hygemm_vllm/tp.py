@@ -90,14 +90,16 @@ def all_reduce_partial(y: torch.Tensor, group: dist.ProcessGroup | None = None) 
 
 
 class PeerExchange:
-    """Buffers of the fused row-parallel GEMM + exchange (`DualLinear.run_exchange`).
+    """Buffers of the row-parallel GEMM + exchange (`DualLinear.run_exchange`).
 
-    Every rank allocates, in memory mapped on all peers (torch symmetric memory over CUDA IPC), a receive
-    buffer of 2 x world x slot_elems elements and a flag array; the GEMM epilogue of rank r stores its
-    partial result into slot r of every rank's buffer over NVLink, and the reduce launch waits on the flags
-    and sums the slots in rank order.  One instance serves every row-parallel layer of a model whose
-    `tokens x outputs` fits `max_elems`, as the exchanges of a stream are ordered.  NVLink multicast is
-    not used (plain peer stores), so the buffers are never bound to a multicast object by this class.
+    Every rank allocates, in memory mapped on all peers (torch symmetric memory over CUDA IPC), an exchange
+    buffer of two halves and a flag array; the GEMM of rank r writes its partial result into one half of
+    rank r's own buffer, and the all-reduce launch tells the peers, waits on the flags, loads every rank's
+    partial over NVLink and sums them in rank order.  One instance serves every row-parallel layer of a model
+    whose `tokens x outputs` fits `max_elems`, as the exchanges of a stream are ordered.  NVLink multicast is
+    not used (plain peer loads), so the buffers are never bound to a multicast object by this class.
+    Callers read `status()` at step boundaries: a peer that did not arrive in time leaves a code there and
+    NaN in that exchange's result.
     """
 
     def __init__(self, group: dist.ProcessGroup, max_elems: int, dtype: torch.dtype, device: torch.device):
@@ -109,17 +111,17 @@ class PeerExchange:
         if self.world > 8:
             raise ValueError("PeerExchange serves at most 8 ranks of one NVLink domain")
         self.dtype, self.group = dtype, group
-        self.slot_elems = -(-max_elems // 8) * 8
-        self.recv = symm.empty(2 * self.world * self.slot_elems, dtype=dtype, device=device)
+        self.half_bytes = -(-max_elems * 2 // 256) * 256          # one half: max_elems 16-bit partial sums
+        self.buffer = symm.empty(2 * self.half_bytes, dtype=torch.uint8, device=device)
         self.flags = symm.empty(64, dtype=torch.int32, device=device)
-        self.recv.zero_()
+        self.buffer.zero_()
         self.flags.zero_()
         self.state = torch.zeros(4, dtype=torch.int32, device=device)
         torch.cuda.synchronize(device)
-        self._handles = (symm.rendezvous(self.recv, group), symm.rendezvous(self.flags, group))
-        self.recv_ptrs = (C.c_void_p * self.world)(*[int(p) for p in self._handles[0].buffer_ptrs])
+        self._handles = (symm.rendezvous(self.buffer, group), symm.rendezvous(self.flags, group))
+        self.buffer_ptrs = (C.c_void_p * self.world)(*[int(p) for p in self._handles[0].buffer_ptrs])
         self.flag_ptrs = (C.c_void_p * self.world)(*[int(p) for p in self._handles[1].buffer_ptrs])
-        if self.recv_ptrs[self.rank] != self.recv.data_ptr():
+        if self.buffer_ptrs[self.rank] != self.buffer.data_ptr():
             raise RuntimeError("symmetric memory did not return this rank's own buffer at its rank index")
         dist.barrier(group)
         torch.cuda.synchronize(device)

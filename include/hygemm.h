@@ -60,7 +60,9 @@ enum { HG_SCHEDULE_AUTO = 0,        /* chosen from the shape and the SM count */
        HG_SCHEDULE_DATA_PARALLEL = 1, /* one work unit per output tile */
        HG_SCHEDULE_SPLIT_K = 2,     /* fixed split of K, deterministic fix-up */
        HG_SCHEDULE_STREAM_K = 3,    /* equal k-block share per CTA */
-       HG_SCHEDULE_SIMT = 28 };     /* SIMT kernel (reference ids 28-34, output_channel_gemv.cu) */
+       HG_SCHEDULE_SIMT = 28 };     /* SIMT kernel: the reference's ids 28-34 (output_channel_gemv.cu) all select it */
+/* The reference's other variant ids (4-27, 35-44: CUTLASS and cp.async tile shapes) are accepted and run with
+ * HG_SCHEDULE_AUTO, so a plan file tuned on the reference's GPU still loads; ids of 45 and above are refused. */
 
 /* integrations/vllm/native/runtime.cu:116 */
 const char* hg_last_error(void);
@@ -90,7 +92,9 @@ int hg_create(int low_id, int high_id, const hg_problem* low, const hg_problem* 
 int hg_create_dtype(int low_id, int high_id, const hg_problem* low, const hg_problem* high, void* stream,
                     int dtype, void** handle);
 /* integrations/vllm/native/runtime.cu:148-149 — rebind pointers (same shape) and
- * enqueue on `stream`; allocates nothing; may be captured in a CUDA graph. */
+ * enqueue on `stream`; allocates nothing; may be captured in a CUDA graph.  The kernel starts reading
+ * weights, weight scales and ids before it waits for the kernel in front of it in the stream, so those must be
+ * complete (not still being written by work queued just before) when the first hg_run on a stream is issued. */
 int hg_run(void* handle, const hg_problem* low, const hg_problem* high, void* stream, int policy);
 /* hg_pack + hg_run in ONE launch for decode sizes (tokens <= 16): `x` is the 16-bit activation matrix
  * [tokens,k] (x_dtype = HG_DTYPE_*); dedicated quantiser warps of the GEMM kernel convert each CTA's K slice with
@@ -130,38 +134,49 @@ int hg_plan(int rows_low, int rows_high, int tokens, int k, int sms, int schedul
  * counters and status words live in one array of HG_STATIC_SCRATCH_BYTES inside the library image.
  *   - `schedule` is an HG_SCHEDULE_* id 0..3, `dtype` an HG_DTYPE_*; inputs and outputs as for hg_run.
  *   - The first call on a device looks up the array's device address and raises the kernel's
- *     shared-memory limit: make that call before any stream capture.
+ *     shared-memory limit.
+ *   - NOT for stream capture: whenever the array holds another shape's schedule the call copies this
+ *     shape's schedule into it from host memory (a copy from pageable memory, which also waits for the
+ *     stream), and a captured copy would replay from memory a later call rewrites.  A capturing stream
+ *     is refused with -1.  Repeating the shape of the previous call on a device copies nothing.
  *   - Every call uses the same array.  Calls on one stream are safe; calls that overlap on the GPU
- *     (different streams or threads) race.  Counters and status are cleared at the start of each call.
+ *     (different streams or threads) race.  Arrival counters are cleared at the start of each call.
  *   - A shape whose schedule and partial sums exceed the array returns -1 with a message naming both
  *     sizes; nothing is launched.  Use hg_create/hg_run for such shapes. */
 int hg_run_static(int schedule, const hg_problem* low, const hg_problem* high, void* stream, int dtype);
+/* hg_status for the hg_run_static calls on the current device since the last read: status[3] = {error code of
+ * a bounded in-kernel wait that gave up (0 = none), K128 blocks issued, work units stored}; clears them and
+ * synchronises `stream`.  Without it an expired wait on this path would go unseen, as there is no handle to ask. */
+int hg_static_status(void* stream, int* status);
 
-/* ---- Row-parallel tensor parallelism: GEMM fused with the exchange of its partial sums over peer memory.
- * No counterpart in the reference, which refuses tensor_parallel_size > 1
- * (integrations/vllm/hygemm_vllm/quantization.py:81-83).
+/* ---- Row-parallel tensor parallelism: the GEMM writes its partial sums into a peer-mapped buffer and a second
+ * kernel pulls and adds the partials of all ranks over NVLink.  No counterpart in the reference, which refuses
+ * tensor_parallel_size > 1 (integrations/vllm/hygemm_vllm/quantization.py:81-83).
  *
- * Every rank owns a receive buffer of 2 x world x slot_elems 16-bit elements and a flag array of `world`
- * ints, both mapped on every peer (CUDA IPC / symmetric memory), plus three private ints of `state`
- * (exchange count, block ticket, status), all zeroed once.  One exchange is two calls on every rank:
+ * Every rank owns an exchange buffer of 2 x half_bytes and a flag array of `world` ints, both mapped on
+ * every peer (CUDA IPC / symmetric memory), plus three private ints of `state` (exchange count, block ticket,
+ * status), all zeroed once.  One exchange is two calls on every rank:
  *
- *   hg_run_push    the GEMM of hg_run (or hg_run_x when `x` is not null), whose epilogue stores this rank's
- *                  partial [tokens,outputs] into slot `rank` of EVERY rank's receive buffer (`recv[w]` =
- *                  base of rank w's buffer as mapped here; recv[rank] is the own one) tile by tile, so the
- *                  NVLink transfer overlaps the main loop.  `output` of the problems is ignored.
- *   hg_tp_reduce   publishes "my partials are written" to every peer's flag array, waits (bounded: about
- *                  one second, then status = 1000 + rank waited for, readable with hg_tp_status) for all
- *                  world flags in the own array, and sums the world slots in rank order into `out`
- *                  (identical bits on every rank).  It then advances `state[0]`.
+ *   hg_run_partial   the GEMM of hg_run (or hg_run_x when `x` is not null), whose scatter epilogue stores this
+ *                    rank's partial [tokens,outputs] into one half of its OWN buffer: 16-bit elements, or fp32
+ *                    when `f32` is set (decode sizes: the sum is then rounded once, not once per rank).
+ *                    `output` of the problems is ignored.
+ *   hg_tp_allreduce  publishes "my partial is written" to every peer's flag array, waits (bounded:
+ *                    HYGEMM_TP_WAIT_MS, default one second; then status = 1000 + rank waited for, readable
+ *                    with hg_tp_status, and `out` is filled with NaN) for all `world` flags in the own array,
+ *                    loads the partials of all ranks (`buffers[w]` = rank w's buffer as mapped here, 16-byte
+ *                    loads over NVLink, all in flight together) and adds them in rank order into `out`:
+ *                    identical bits on every rank.  It then advances `state[0]`.
  *
- * The two halves of the receive buffer are used alternately (by the parity of state[0] + 1), which is
- * what makes the next exchange safe to start while a slow peer still sums the previous one.  Both calls
- * allocate nothing and are graph-capturable: the exchange count lives in device memory.  world <= 8. */
+ * The two halves of a buffer are used alternately (by the parity of state[0] + 1): a rank can only reach the
+ * GEMM that overwrites a half after every peer has published the exchange in between, i.e. after every peer
+ * has finished reading that half.  Both calls allocate nothing and are graph-capturable: the exchange count
+ * lives in device memory.  world <= 8.  Callers poll hg_tp_status at step boundaries. */
 #define HG_TP_MAX_WORLD 8
-int hg_run_push(void* handle, const hg_problem* low, const hg_problem* high, const void* x, int x_dtype,
-                void* const* recv, int world, int rank, int64_t slot_elems, const int* state, void* stream);
-int hg_tp_reduce(const void* recv_own, void* out, int64_t elems, int64_t slot_elems, int world, int rank,
-                 int* const* flags, int* state, int dtype, void* stream);
+int hg_run_partial(void* handle, const hg_problem* low, const hg_problem* high, const void* x, int x_dtype,
+                   void* buffer, int64_t half_bytes, int f32, const int* state, void* stream);
+int hg_tp_allreduce(void* const* buffers, void* out, int64_t elems, int64_t half_bytes, int f32, int world, int rank,
+                    int* const* flags, int* state, int dtype, void* stream);
 /* Reads and clears state[2] (0 = every wait was satisfied). */
 int hg_tp_status(int* state, void* stream, int* status);
 

@@ -1,11 +1,12 @@
-"""Row-parallel exchange (hg_run_push + hg_tp_reduce) on ONE GPU.
+"""Row-parallel exchange (hg_run_partial + hg_tp_allreduce) on ONE GPU.
 
 Two ranks are emulated by two sets of buffers in the same device memory and launches in an order in
-which no launch ever waits for a later one: both GEMMs push first, the flag the first reduce would wait
-for is written by the host beforehand (standing in for the other rank's publish), and the second reduce
-finds the first one's publish already there.  The sum must equal the fp32 sum of the two partial results
-rounded once, bit for bit, on both ranks and across two consecutive exchanges (both halves of the
-receive buffers).  The real multi-GPU path is exercised by `bench.py --gpus N`.
+which no launch ever waits for a later one: both GEMMs write their partials first, the flag the first
+all-reduce would wait for is written by the host beforehand (standing in for the other rank's publish), and
+the second all-reduce finds the first one's publish already there.  The sum must equal the fp32 sum of the
+two partial results rounded once (the partials themselves cross as fp32 at decode sizes and as 16-bit values
+above), bit for bit, on both ranks and across three consecutive exchanges (both halves of the exchange
+buffers).  The real multi-GPU path is exercised by `bench.py --gpus N`.
 """
 import ctypes as C
 
@@ -21,10 +22,10 @@ pytestmark = pytest.mark.gpu
 class LocalExchange:
     """Stand-in for tp.PeerExchange with every rank's buffers on this GPU."""
 
-    def __init__(self, world, rank, slot_elems, recv, flags, dtype):
-        self.world, self.rank, self.slot_elems, self.dtype = world, rank, slot_elems, dtype
-        self.recv = recv[rank]
-        self.recv_ptrs = (C.c_void_p * world)(*[t.data_ptr() for t in recv])
+    def __init__(self, world, rank, half_bytes, buffers, flags, dtype):
+        self.world, self.rank, self.half_bytes, self.dtype = world, rank, half_bytes, dtype
+        self.buffer = buffers[rank]
+        self.buffer_ptrs = (C.c_void_p * world)(*[t.data_ptr() for t in buffers])
         self.flag_ptrs = (C.c_void_p * world)(*[t.data_ptr() for t in flags])
         self.state = torch.zeros(4, dtype=torch.int32, device="cuda")
 
@@ -44,10 +45,10 @@ def shards(tokens, k, outputs, high, world, dtype):
     return layers, xs
 
 
-def buffers(world, slot, dtype):
-    recv = [torch.full((2 * world * slot,), float("nan"), dtype=dtype, device="cuda") for _ in range(world)]
+def buffers(world, half_bytes):
+    bufs = [torch.full((2 * half_bytes,), 0xFF, dtype=torch.uint8, device="cuda") for _ in range(world)]   # NaN patterns
     flags = [torch.zeros(64, dtype=torch.int32, device="cuda") for _ in range(world)]
-    return recv, flags
+    return bufs, flags
 
 
 @pytest.mark.parametrize("tokens,fused", [(1, True), (16, True), (16, False), (48, False), (100, False), (128, False), (130, False)])
@@ -55,28 +56,46 @@ def buffers(world, slot, dtype):
 def test_two_emulated_ranks_sum_bit_exact(tokens, fused, dtype):
     world, k, outputs, high = 2, 1024, 640, 96
     layers, xs = shards(tokens, k, outputs, high, world, dtype)
-    slot = -(-tokens * outputs // 8) * 8
-    recv, flags = buffers(world, slot, dtype)
-    ex = [LocalExchange(world, r, slot, recv, flags, dtype) for r in range(world)]
+    elems = tokens * outputs
+    f32 = int(tokens <= 16)
+    half = -(-elems * 4 // 256) * 256
+    bufs, flags = buffers(world, half)
+    ex = [LocalExchange(world, r, half, bufs, flags, dtype) for r in range(world)]
     lib, stream = native.library(), torch.cuda.current_stream().cuda_stream
     for epoch in (1, 2, 3):
         packed = [native.pack(x) for x in xs]
-        partial = [layers[r].run_packed(*packed[r]) for r in range(world)]
-        want = (partial[0].float() + partial[1].float()).to(dtype)
+        if f32:
+            # the partial sums cross as fp32: the reference sum is built from fp32 partials too
+            partial32 = []
+            for r in range(world):
+                layer, (q, sf) = layers[r], packed[r]
+                out32 = torch.zeros(2 * half, dtype=torch.uint8, device="cuda")
+                st = torch.zeros(4, dtype=torch.int32, device="cuda")
+                y0 = torch.empty(tokens, outputs, dtype=dtype, device="cuda")
+                low, high_p = layer.problems(q, sf, y0)
+                layer.run_packed(q, sf)                                   # warms the handle
+                handle = layer.handles[next(k_ for k_ in layer.handles if k_[0] == tokens)]
+                native.check(lib.hg_run_partial(handle, C.byref(low), C.byref(high_p), None, 0, out32.data_ptr(), half, 1,
+                                                st.data_ptr(), stream))
+                partial32.append(out32[half:half + elems * 4].view(torch.float32).clone())   # exchange 1 -> second half
+            want = (partial32[0] + partial32[1]).to(dtype).view(tokens, outputs)
+        else:
+            partial = [layers[r].run_packed(*packed[r]) for r in range(world)]
+            want = (partial[0].float() + partial[1].float()).to(dtype)
         flags[0][1] = epoch                       # rank 1's publish, ahead of time
         ys = [torch.empty(tokens, outputs, dtype=dtype, device="cuda") for _ in range(world)]
-        handles = []
-        for r in range(world):                    # both GEMMs push before any reduce runs
+        for r in range(world):                    # both GEMMs write their partials before any all-reduce runs
             layer, (q, sf) = layers[r], packed[r]
             low, high_p = layer.problems(xs[r] if fused else q, xs[r] if fused else sf, ys[r])
+            if not layer.handles:
+                layer.run_packed(q, sf)
             handle = layer.handles[next(k_ for k_ in layer.handles if k_[0] == tokens)]
-            native.check(lib.hg_run_push(handle, C.byref(low), C.byref(high_p), xs[r].data_ptr() if fused else None,
-                                         native.DTYPES[dtype], ex[r].recv_ptrs, world, r, slot,
-                                         ex[r].state.data_ptr(), stream))
-            handles.append(handle)
+            native.check(lib.hg_run_partial(handle, C.byref(low), C.byref(high_p), xs[r].data_ptr() if fused else None,
+                                            native.DTYPES[dtype], bufs[r].data_ptr(), half, f32,
+                                            ex[r].state.data_ptr(), stream))
         for r in range(world):
-            native.check(lib.hg_tp_reduce(recv[r].data_ptr(), ys[r].data_ptr(), tokens * outputs, slot, world, r,
-                                          ex[r].flag_ptrs, ex[r].state.data_ptr(), native.DTYPES[dtype], stream))
+            native.check(lib.hg_tp_allreduce(ex[r].buffer_ptrs, ys[r].data_ptr(), elems, half, f32, world, r,
+                                             ex[r].flag_ptrs, ex[r].state.data_ptr(), native.DTYPES[dtype], stream))
         torch.cuda.synchronize()
         for r in range(world):
             assert ex[r].status() == 0
@@ -87,9 +106,9 @@ def test_two_emulated_ranks_sum_bit_exact(tokens, fused, dtype):
 
 def test_single_rank_exchange_equals_plain_run():
     layers, xs = shards(16, 512, 384, 40, 1, torch.bfloat16)
-    slot = 16 * 384
-    recv, flags = buffers(1, slot, torch.bfloat16)
-    ex = LocalExchange(1, 0, slot, recv, flags, torch.bfloat16)
+    half = 16 * 384 * 4
+    bufs, flags = buffers(1, half)
+    ex = LocalExchange(1, 0, half, bufs, flags, torch.bfloat16)
     want = layers[0](xs[0])
     for _ in range(2):
         got = layers[0].run_exchange(ex, x=xs[0])
@@ -101,19 +120,20 @@ def test_single_rank_exchange_equals_plain_run():
 
 
 def test_missing_peer_ends_the_wait_with_a_status():
-    """A flag that nothing sets: the reduce gives up after its limit (about a second), reports which
-    rank it waited for, leaves the output alone, still advances the exchange count and the context stays usable."""
+    """A flag that nothing sets: the all-reduce gives up after its limit (about a second), reports which rank it
+    waited for, fills the output with NaN so the failure cannot pass for a result, still advances the exchange
+    count and the context stays usable."""
     world, tokens, outputs = 2, 8, 256
-    slot = tokens * outputs
-    recv, flags = buffers(world, slot, torch.bfloat16)
-    ex = LocalExchange(world, 0, slot, recv, flags, torch.bfloat16)
+    half = tokens * outputs * 4
+    bufs, flags = buffers(world, half)
+    ex = LocalExchange(world, 0, half, bufs, flags, torch.bfloat16)
     out = torch.full((tokens, outputs), 7.0, dtype=torch.bfloat16, device="cuda")
-    native.check(native.library().hg_tp_reduce(recv[0].data_ptr(), out.data_ptr(), tokens * outputs, slot, world, 0,
-                                               ex.flag_ptrs, ex.state.data_ptr(), 1, torch.cuda.current_stream().cuda_stream))
+    native.check(native.library().hg_tp_allreduce(ex.buffer_ptrs, out.data_ptr(), tokens * outputs, half, 1, world, 0,
+                                                  ex.flag_ptrs, ex.state.data_ptr(), 1, torch.cuda.current_stream().cuda_stream))
     torch.cuda.synchronize()
     assert ex.status() == 1001
     assert ex.status() == 0
-    assert (out == 7.0).all() and ex.state[0].item() == 1
+    assert torch.isnan(out.float()).all() and ex.state[0].item() == 1
     assert torch.ones(4, device="cuda").sum().item() == 4.0
 
 

@@ -204,14 +204,29 @@ def test_row_parallel_shards_and_l2norm_rule():
 
 
 def test_exchange_arguments_are_checked():
-    """hg_run_push / hg_tp_reduce refuse bad arguments before touching a device."""
+    """hg_run_partial / hg_tp_allreduce refuse bad arguments before touching a device."""
     lib = native.library()
-    flags = (C.c_void_p * 2)(16, 16)
-    assert lib.hg_tp_reduce(None, None, 8, 8, 2, 0, flags, None, 1, None) == -1
-    assert lib.hg_tp_reduce(16, 16, 12, 16, 2, 0, flags, 16, 1, None) == -1
-    assert b"multiples of 8" in lib.hg_last_error()
-    assert lib.hg_tp_reduce(16, 16, 8, 8, 9, 0, flags, 16, 1, None) == -1
-    assert lib.hg_run_push(None, None, None, None, 0, None, 2, 0, 8, None, None) == -1
+    ptrs = (C.c_void_p * 2)(16, 16)
+    assert lib.hg_tp_allreduce(None, None, 8, 16, 0, 2, 0, ptrs, None, 1, None) == -1
+    assert lib.hg_tp_allreduce(ptrs, 16, 12, 32, 0, 2, 0, ptrs, 16, 1, None) == -1
+    assert b"multiple of 8" in lib.hg_last_error()
+    assert lib.hg_tp_allreduce(ptrs, 16, 8, 16, 1, 2, 0, ptrs, 16, 1, None) == -1      # 8 fp32 values do not fit 16 bytes
+    assert lib.hg_tp_allreduce(ptrs, 16, 8, 16, 0, 9, 0, ptrs, 16, 1, None) == -1
+    assert lib.hg_run_partial(None, None, None, None, 0, None, 16, 0, None, None) == -1
+
+
+def test_gemm_arguments_are_checked_on_every_policy():
+    """A null or misaligned pointer is an error on the SIMT policies too, never a launch (no GPU needed: the
+    check runs before anything is enqueued; the handle itself needs a device, so only hg_run_static is used)."""
+    lib = native.library()
+    bad = native.Problem(128, 4, 256, 128, None, None, None, None, None, None)
+    assert lib.hg_run_static(0, C.byref(bad), C.byref(bad), None, 1) == -1
+    assert b"Null pointer" in lib.hg_last_error() or b"share" in lib.hg_last_error()
+    odd = native.Problem(128, 4, 256, 128, 64, 24, 64, 64, 64, 64)       # activation codes not 16-byte aligned
+    none = native.Problem(0, 4, 256, 128, None, None, None, None, None, None)
+    assert lib.hg_run_static(0, C.byref(odd), C.byref(none), None, 1) == -1
+    assert b"aligned" in lib.hg_last_error()
+    assert lib.hg_static_status(None, None) == -1
 
 
 def test_tuner_candidates_and_plan_binding(tmp_path):

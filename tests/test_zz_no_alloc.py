@@ -83,3 +83,53 @@ def test_shape_beyond_the_static_array_is_refused():
     bad = native.Problem()
     assert lib.hg_run_static(0, C.byref(bad), C.byref(bad), None, 1) == -1
     assert lib.hg_run_static(9, None, None, None, 1) == -1
+
+
+def test_static_path_allocates_nothing_reports_its_status_and_refuses_capture():
+    """Free device memory is the same before and after the calls (first call included: its set-up only looks
+    up an address); the status words of the array have their own reader, so a bounded wait that expired on
+    this path would be seen; and a capturing stream is refused, because the call copies a schedule from host
+    memory that a later call rewrites."""
+    lib = native.library()
+    case = _operands(16, 3584, 3584, 384)
+    torch.cuda.synchronize()
+    status = (C.c_int * 3)()
+    stream = torch.cuda.current_stream().cuda_stream
+    native.check(lib.hg_static_status(stream, status))            # also performs the per-device set-up
+    free_before, _ = torch.cuda.mem_get_info()
+    other = _operands(4, 896, 640, 64)                              # torch allocations happen out here, not inside
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    d = {n: dev(case[n]) for n in ("w4", "sf4", "lo", "w8", "sf8", "hi", "xq", "xsf")}
+    e = {n: dev(other[n]) for n in ("w4", "sf4", "lo", "w8", "sf8", "hi", "xq", "xsf")}
+    y = torch.zeros(16 * 3584, dtype=torch.int16, device="cuda")
+    y2 = torch.zeros(4 * 640, dtype=torch.int16, device="cuda")
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+
+    def problems(t, tokens, k, outputs, out):
+        low = native.Problem(t["lo"].numel(), tokens, k, outputs, t["w4"].data_ptr(), t["xq"].data_ptr(), t["sf4"].data_ptr(),
+                             t["xsf"].data_ptr(), t["lo"].data_ptr(), out.data_ptr())
+        high = native.Problem(t["hi"].numel(), tokens, k, outputs, t["w8"].data_ptr(), t["xq"].data_ptr(), t["sf8"].data_ptr(),
+                              t["xsf"].data_ptr(), t["hi"].data_ptr(), out.data_ptr())
+        return low, high
+    big, small = problems(d, 16, 3584, 3584, y), problems(e, 4, 896, 640, y2)
+    for low, high in (big, small, big, small):                      # alternating shapes: schedules come from the cache
+        native.check(lib.hg_run_static(0, C.byref(low), C.byref(high), stream, 1))
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    native.check(lib.hg_static_status(stream, status))
+    tiles_big = -(-d["lo"].numel() // 128) + -(-d["hi"].numel() // 128)
+    tiles_small = -(-e["lo"].numel() // 128) + -(-e["hi"].numel() // 128)
+    assert status[0] == 0
+    assert status[1] == 2 * (tiles_big * (3584 // 128) + tiles_small * (896 // 128))     # K128 blocks issued
+    native.check(lib.hg_static_status(stream, status))
+    assert list(status) == [0, 0, 0]                                                      # cleared by the read
+    graph = torch.cuda.CUDAGraph()
+    with pytest.raises(RuntimeError, match="cannot be captured"):
+        with torch.cuda.graph(graph):
+            low, high = big
+            native.check(lib.hg_run_static(0, C.byref(low), C.byref(high), torch.cuda.current_stream().cuda_stream, 1))
+    torch.cuda.synchronize()
+    assert torch.ones(4, device="cuda").sum().item() == 4.0
