@@ -66,6 +66,18 @@ def gemm_bytes(m, k, n, h):
     return low * k // 2 + h * k + n * k // 32 + 4 * n + m * k + m * k // 32 + 2 * m * n
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of the same launch, from the ncu
+# captures summarised under profiles/ (one per shape class; cold weights, weight copies cycled).  The ratio
+# does not move with the token count inside a class: the weights are read once and dominate.
+DRAM_TRAFFIC_RATIO = {("gate_up", "decode"): 1.01, ("down", "decode"): 1.00, ("qkv", "decode"): 0.99,
+                      ("o_proj", "decode"): 0.99, ("gate_up", "wide"): 1.01, ("down", "wide"): 1.00,
+                      ("qkv", "wide"): 0.99, ("o_proj", "wide"): 0.99}
+
+
+def dram_traffic_ratio(name: str, m: int) -> float:
+    return DRAM_TRAFFIC_RATIO[(name, "decode" if m <= 32 else "wide")]
+
+
 def k_block_shard(k: int, rank: int, world: int) -> tuple[int, int]:
     """Row-parallel K range of `rank`, in whole K128 blocks (uneven when blocks % world != 0)."""
     blocks = k // 128
@@ -482,6 +494,43 @@ def run_single_gemm(args, device):
                       "status": [layer.status() for layer in layers][:2]}))
 
 
+def run_single_quant(args, device):
+    """`--quant act:ROWS:K` or `--quant silu:ROWS:K`: the activation quantiser or the SwiGLU + quantiser alone,
+    `steps` launches as one CUDA graph over enough distinct inputs to exceed L2; one JSON line (a small,
+    self-ending case for ncu captures)."""
+    from hygemm_vllm import native, producer
+    kind, rows, k = args.quant.split(":")
+    rows, k = int(rows), int(k)
+    width = 2 * k if kind == "silu" else k
+    in_bytes = rows * width * 2
+    copies = max(2, min(64, -(-300_000_000 // max(in_bytes, 1))))
+    g = torch.Generator().manual_seed(SEED)
+    xs = [(torch.randn(rows, width, generator=g) * (2.0 if kind == "silu" else 1.0)).to(torch.bfloat16).to(device)
+          for _ in range(copies)]
+
+    def call(x):
+        return producer.silu_pack(x, 0) if kind == "silu" else native.pack(x)
+    count = max(args.steps, copies)
+    keep = [call(x) for x in xs]
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        keep = [call(xs[i % copies]) for i in range(count)]
+    times = []
+    for _ in range(6):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b) * 1e-3 / count)
+    seconds = statistics.median(times[1:])
+    nbytes = in_bytes + rows * k + rows * k // 32
+    print(json.dumps({"quant": kind, "rows": rows, "K": k, "copies": copies, "us_median": seconds * 1e6,
+                      "GBps": nbytes / seconds / 1e9, "algorithmic_bytes": nbytes}))
+
+
 # ------------------------------------------------------------------------------------------------
 # main
 # ------------------------------------------------------------------------------------------------
@@ -495,6 +544,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--gemm", default=None, metavar="NAME:M[:SCHEDULE[:HIGH_FRACTION[:fused]]]",
                     help="profiling aid: run only this GEMM (e.g. gate_up:16) a few times on cold weights and exit")
+    ap.add_argument("--quant", default=None, metavar="act|silu:ROWS:K",
+                    help="profiling aid: run only this quantiser launch a few times on cold inputs and exit")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     rank = int(os.environ.get("RANK", "0"))
@@ -511,6 +562,9 @@ def main():
     device = torch.device("cuda", local)
     if args.gemm:
         run_single_gemm(args, device)
+        return
+    if args.quant:
+        run_single_quant(args, device)
         return
     import torch.distributed as dist
     group = None
@@ -647,6 +701,69 @@ def main():
         torch.cuda.synchronize()
         for name, m, a, b in events:
             per.setdefault((name, m), []).append(a.elapsed_time(b) * 1e-3)
+    # ---- hot (L2-resident) figure per shape: the same GEMM on the same weights, back to back in one graph.
+    # gate_up (79 MB of weights) only just fits the 126 MB L2; the other three stay resident.
+    hot = {}
+    try:
+        from hygemm_vllm import native as _native
+        for m in M_SWEEP:
+            x = sweep.dev[m]
+            gate_up_out = layers[0]["gate_up"].run_packed(*_native.pack(x["x_gate"]))
+            packed = {"qkv": _native.pack(x["x_qkv"]), "o_proj": _native.pack(x["x_o"]), "gate_up": _native.pack(x["x_gate"]),
+                      "down": sweep.producer.silu_pack(gate_up_out, 0)}
+            for name in SHAPES:
+                if world > 1 and name in ROW_PARALLEL:
+                    continue                                   # the exchange needs every rank in step: cold rows only
+                rt, (q, sf) = layers[0][name], packed[name]
+                rt.run_packed(q, sf)
+                torch.cuda.synchronize()
+                burst = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(burst):
+                    for _ in range(10):
+                        rt.run_packed(q, sf)
+                samples = []
+                for _ in range(4):
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    burst.replay()
+                    b.record()
+                    torch.cuda.synchronize()
+                    samples.append(a.elapsed_time(b) * 1e-3 / 10)
+                hot[(name, m)] = statistics.median(samples[1:])
+                del burst
+    except Exception as exc:                                   # never lose the main line to the diagnostic rows
+        hot = {}
+        print(f"hot rows skipped: {type(exc).__name__}: {exc}", file=sys.stderr)
+    # ---- prefill buckets (the reference's plans reach 2048 tokens): the same kernel in rows of 128-token
+    # tiles, the two weight sets alternating so the weights come from HBM; outside the step and its metric.
+    prefill = []
+    if world == 1:
+        try:
+            from hygemm_vllm import native as _native
+            g2 = torch.Generator().manual_seed(SEED + 7)
+            for m in (256, 1024, 2048):
+                for name, (k, _parts) in SHAPES.items():
+                    q, sf = _native.pack(torch.randn(m, k, generator=g2).to(torch.bfloat16).to(device))
+                    for layer in layers:
+                        layer[name].run_packed(q, sf)
+                    torch.cuda.synchronize()
+                    burst = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(burst):
+                        for i in range(4):
+                            layers[i % 2][name].run_packed(q, sf)
+                    samples = []
+                    for _ in range(4):
+                        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        a.record()
+                        burst.replay()
+                        b.record()
+                        torch.cuda.synchronize()
+                        samples.append(a.elapsed_time(b) * 1e-3 / 4)
+                    del burst
+                    prefill.append((name, m, statistics.median(samples[1:])))
+        except Exception as exc:
+            prefill = []
+            print(f"prefill rows skipped: {type(exc).__name__}: {exc}", file=sys.stderr)
     status = [rt.status() for layer in layers for rt in layer.values()]
     if any(s[0] for s in status):
         raise SystemExit(f"device reported a stuck wait: {status}")
@@ -659,16 +776,29 @@ def main():
         if peaks_file.exists():
             peaks = json.loads(peaks_file.read_text())
         hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
-        sweep_rows, bytes_sum, time_sum = [], 0, 0.0
+        # Dense FP8 tensor peak: none is measured on this pool, so twice the measured bf16 cuBLAS burst figure
+        # stands in (FP8 issues at twice the bf16 rate), as `tensor_peak_source` says.
+        tensor_peak = 2.0 * float(peaks.get("bf16_tflops", 1590.0))
+        sweep_rows, bytes_sum, time_sum, traffic_sum = [], 0, 0.0, 0.0
         for (name, m), durations in sorted(per.items(), key=lambda kv: (list(SHAPES).index(kv[0][0]), kv[0][1])):
             k, n, h = stats[name]
             seconds = statistics.median(durations)
             nbytes = gemm_bytes(m, k, n, h)
             bytes_sum += nbytes
             time_sum += seconds
-            sweep_rows.append({"gemm": name, "M": m, "K": k, "N": n, "H": h, "us": round(seconds * 1e6, 2),
-                               "GBps": round(nbytes / seconds / 1e9, 1), "TFLOPs": round(2 * m * n * k / seconds / 1e12, 2),
-                               "hbm_frac": round(nbytes / seconds / 1e9 / hbm_peak, 3)})
+            traffic_sum += nbytes * dram_traffic_ratio(name, m)
+            flops = 2 * m * n * k
+            row = {"gemm": name, "M": m, "K": k, "N": n, "H": h, "us": round(seconds * 1e6, 2),
+                   "GBps": round(nbytes / seconds / 1e9, 1), "TFLOPs": round(flops / seconds / 1e12, 2),
+                   "hbm_frac": round(nbytes / seconds / 1e9 / hbm_peak, 3)}
+            if (name, m) in hot:
+                hs = hot[(name, m)]
+                row.update({"hot_us": round(hs * 1e6, 2), "hot_TFLOPs": round(flops / hs / 1e12, 2)})
+            if m >= 64:                                       # the tensor-pipe side of the roofline, cold and hot
+                row["tensor_frac"] = round(flops / seconds / 1e12 / tensor_peak, 3)
+                if (name, m) in hot:
+                    row["hot_tensor_frac"] = round(flops / hot[(name, m)] / 1e12 / tensor_peak, 3)
+            sweep_rows.append(row)
         # Two figures for the same 32 GEMM launches.  `bracketed`: each launch between its own pair of event
         # nodes, which serialises it against its neighbours (no programmatic overlap of prologue and tail) and
         # adds the event nodes' own cost, so the durations sum to more than the step.  `achieved`: the GEMM
@@ -698,18 +828,34 @@ def main():
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                          "frac": achieved / hbm_peak,
                          "bracketed": {"achieved": bracketed, "frac": bracketed / hbm_peak},
-                         # ncu captures of gate_up and down at M=16 read 1.01x and 1.00x the algorithmic bytes from
-                         # DRAM; traffic grows with the bytes streamed, so the step average is scaled by that ratio.
-                         "traffic": 1.01 * bytes_sum / len(sweep_rows), "traffic_unit": "bytes per GEMM launch (mean)",
+                         # DRAM bytes per launch: algorithmic bytes of each launch times the read+write ratio its
+                         # shape class showed under ncu (`dram_traffic_ratio`), averaged over the step's GEMM launches.
+                         "traffic": traffic_sum / len(sweep_rows), "traffic_unit": "bytes per GEMM launch (mean)",
+                         "tensor_peak": tensor_peak, "tensor_peak_unit": "TFLOP/s",
+                         "tensor_peak_source": "2 x measured bf16 cuBLAS burst (no FP8 peak is measured on this pool)"
+                                               if peaks else "2 x fallback bf16 figure",
                          "kernel": "hybrid_gemm_tc_kernel", "peak_source": "of measured" if peaks else "of fallback",
                          "how": "achieved: algorithmic bytes of the 32 GEMM launches of a step / CUDA-event time of "
                                 "the whole timed step (quantiser launches included in the time); bracketed: the same "
                                 "bytes / sum of the launches' median CUDA-event durations, " + how},
             "sweep": sweep_rows,
+            "prefill": [{"gemm": name, "M": m, "us": round(sec * 1e6, 1),
+                         "TFLOPs": round(2 * m * stats[name][1] * stats[name][0] / sec / 1e12, 1),
+                         "tensor_frac": round(2 * m * stats[name][1] * stats[name][0] / sec / 1e12 / tensor_peak, 3)}
+                        for name, m, sec in prefill],
         }
         if not args.no_cpu_baseline and world == 1:
             cpu_reference_sample()
             line["cpu_baseline"], _ = cpu_reference_sample(min_seconds=10.0)
+            # The GPU on EXACTLY the CPU sample (qkv + o_proj at 1, 16 and 128 tokens, cold weights), so one
+            # like-for-like quotient stands beside the whole-sweep value.
+            same = [r for r in sweep_rows if r["gemm"] in ("qkv", "o_proj") and r["M"] in (1, 16, 128)]
+            if len(same) == 6:
+                gpu_same = sum(2 * r["M"] * r["N"] * r["K"] for r in same) / sum(r["us"] for r in same) / 1e6
+                line["cpu_baseline"]["gpu_on_same_sample"] = {"value": gpu_same, "unit": "TFLOP/s",
+                                                              "ratio": gpu_same / line["cpu_baseline"]["value"],
+                                                              "how": "the six GEMM launches of the sample, cold weights, "
+                                                                     "per-launch CUDA-event durations from the step"}
         print(json.dumps(line))
     if world > 1:
         # Graphs that captured NCCL kernels must go before the communicator; a watchdog ends the process
