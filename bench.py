@@ -531,6 +531,34 @@ def run_single_quant(args, device):
                       "GBps": nbytes / seconds / 1e9, "algorithmic_bytes": nbytes}))
 
 
+def run_single_clip(args, device):
+    """`--clip ROWS:K`: the offline MXFP4 exponent search (`hg_clip_pack`) on a seeded random weight matrix, timed
+    with CUDA events; one JSON line with the kernel's rate (it reads 2 B and writes 0.53 B per weight) and the
+    error statistics of the search (a small, self-ending case for ncu captures of the load-time path)."""
+    import ctypes as C
+    from hygemm_vllm import fp4_quant, native
+    rows, k = (int(v) for v in args.clip.split(":"))
+    g = torch.Generator().manual_seed(SEED)
+    w = (torch.randn(rows, k, generator=g) * 0.02).to(torch.bfloat16).to(device)
+    importance = (torch.rand(k, generator=g) * 2).to(device)
+    q4, scales, stats = fp4_quant.quantize(w, importance)
+    lib = native.library()
+    shifts = (C.c_int * 3)(0, -1, -2)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    times = []
+    for _ in range(max(3, args.steps)):
+        start.record()
+        native.check(lib.hg_clip_pack(w.data_ptr(), importance.data_ptr(), q4.data_ptr(), scales.data_ptr(), rows, k,
+                                      shifts, 3, native.DTYPES[w.dtype], torch.cuda.current_stream().cuda_stream))
+        stop.record()
+        stop.synchronize()
+        times.append(start.elapsed_time(stop) * 1e-3)
+    seconds = statistics.median(times)
+    moved = w.numel() * 2 + q4.numel() + scales.numel()
+    print(json.dumps({"rows": rows, "k": k, "us": seconds * 1e6, "GBps": moved / seconds / 1e9,
+                      "algorithmic_bytes": moved, **stats}))
+
+
 # ------------------------------------------------------------------------------------------------
 # main
 # ------------------------------------------------------------------------------------------------
@@ -546,6 +574,8 @@ def main():
                     help="profiling aid: run only this GEMM (e.g. gate_up:16) a few times on cold weights and exit")
     ap.add_argument("--quant", default=None, metavar="act|silu:ROWS:K",
                     help="profiling aid: run only this quantiser launch a few times on cold inputs and exit")
+    ap.add_argument("--clip", default=None, metavar="ROWS:K",
+                    help="profiling aid: time the offline MXFP4 exponent search on a random ROWS x K matrix and exit")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     rank = int(os.environ.get("RANK", "0"))
@@ -565,6 +595,9 @@ def main():
         return
     if args.quant:
         run_single_quant(args, device)
+        return
+    if args.clip:
+        run_single_clip(args, device)
         return
     import torch.distributed as dist
     group = None

@@ -96,38 +96,3 @@ def quantize(w: torch.Tensor, importance: torch.Tensor | None = None, offsets=(0
              "weight_error_before": before.double().sum().item(),
              "weight_error_after": after.double().sum().item()}
     return q4, scales, stats
-
-
-def main(argv=None):
-    """`python -m hygemm_vllm.fp4_quant --rows 37888 --k 3584`: quantise a seeded random matrix with and without
-    the search, print the statistics and the kernel's rate (reads 2 B, writes 0.53 B per weight)."""
-    import argparse
-    import json
-    ap = argparse.ArgumentParser(description="Offline MXFP4 exponent search on a seeded random matrix")
-    ap.add_argument("--rows", type=int, default=37888)
-    ap.add_argument("--k", type=int, default=3584)
-    ap.add_argument("--repeats", type=int, default=5)
-    args = ap.parse_args(argv)
-    g = torch.Generator().manual_seed(20261024)
-    w = (torch.randn(args.rows, args.k, generator=g) * 0.02).to(torch.bfloat16).cuda()
-    importance = (torch.rand(args.k, generator=g) * 2).cuda()
-    q4, scales, stats = quantize(w, importance)
-    lib = native.library()
-    shifts = (C.c_int * 3)(0, -1, -2)
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    times = []
-    for _ in range(args.repeats):
-        start.record()
-        native.check(lib.hg_clip_pack(w.data_ptr(), importance.data_ptr(), q4.data_ptr(), scales.data_ptr(), args.rows, args.k,
-                                      shifts, 3, native.DTYPES[w.dtype], torch.cuda.current_stream().cuda_stream))
-        stop.record()
-        stop.synchronize()
-        times.append(start.elapsed_time(stop) * 1e-3)
-    seconds = sorted(times)[len(times) // 2]
-    moved = w.numel() * 2 + q4.numel() + scales.numel()
-    print(json.dumps({"rows": args.rows, "k": args.k, "us": seconds * 1e6, "GBps": moved / seconds / 1e9,
-                      "algorithmic_bytes": moved, **stats}))
-
-
-if __name__ == "__main__":
-    main()
