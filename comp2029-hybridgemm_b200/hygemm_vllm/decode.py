@@ -5,11 +5,14 @@ token-id prompts, pure-decode timing through the worker extension) for models th
 architecture: weights are vLLM's dummy initialisation, the MXFP8 channels of every linear are the 10 % of
 output channels with the largest weight-row L2 norm (quota rounded to 128), chosen at load time.
 
-    python -m hygemm_vllm.decode --arch qwen2.5-7b --batch 1,16,128 --prompt 128 --steps 128 [--dense]
+    python -m hygemm_vllm.decode --arch qwen2.5-7b --batch 1,16,128 --prompt 128,1024 --steps 128 [--dense]
 
-prints one JSON line per batch size: decode tokens/s over the span of the timed steps (engine gaps
-included), milliseconds per step and the audit of the hybrid layers.  `--dense` serves the same model with
-plain bf16 linears for comparison.
+prints one JSON line per (prompt length, batch size): decode tokens/s from the median milliseconds per step
+over the span of the timed steps (engine gaps included), the coefficient of variation of the samples, and the
+audit of the hybrid layers.  Per cell the reference's protocol (formal/benchmark.py:76-91): one warm-up
+generation, then `--samples` timed ones; a cell whose coefficient of variation exceeds `--cv` is repeated, at
+most three attempts.  `--dense` serves the same model with plain bf16 linears for comparison; `--table FILE`
+appends the rows as a markdown table.
 """
 from __future__ import annotations
 
@@ -78,7 +81,20 @@ def ensure_plugin_entry_point() -> None:
     sys.path.insert(0, str(root))
 
 
-def run(arch: str, batches, prompt: int, steps: int, dense: bool = False, layers: int | None = None, tp: int = 1):
+def summarise(samples: list[dict], batch: int) -> dict:
+    """Median, coefficient of variation and tokens/s of one cell's samples (reference: formal/benchmark.py:84-89)."""
+    import statistics
+    times = [x["decode_ms_per_step"] for x in samples]
+    median = statistics.median(times)
+    cv = statistics.pstdev(times) / statistics.mean(times) if len(times) > 1 else 0.0
+    return {"median_ms_per_step": median, "cv": cv, "decode_tokens_per_s": batch * 1000.0 / median,
+            "steps": min(x["steps"] for x in samples), "graph_steps": min(x["graph_steps"] for x in samples),
+            "gpu_ms_per_step": statistics.median(x["sum_step_gpu_ms"] / x["steps"] for x in samples),
+            "context": [min(x["context_min"] for x in samples), max(x["context_max"] for x in samples)]}
+
+
+def run(arch: str, batches, prompts, steps: int, dense: bool = False, layers: int | None = None, tp: int = 1,
+        samples: int = 5, cv_gate: float = 0.05, attempts: int = 3):
     import torch
     if tp == 1:
         os.environ.setdefault("VLLM_ENABLE_V1_MULTIPROCESSING", "0")   # engine in this process: the plugin is registered here
@@ -87,43 +103,70 @@ def run(arch: str, batches, prompt: int, steps: int, dense: bool = False, layers
     import hygemm_vllm
     hygemm_vllm.register()
     from vllm import LLM, SamplingParams
+    prompts = [prompts] if isinstance(prompts, int) else list(prompts)
     results = []
     with tempfile.TemporaryDirectory() as tmp:
         model_dir = write_model_dir(Path(tmp) / arch, arch, dense, layers=layers)
-        llm = LLM(**engine_arguments(model_dir, batches, prompt, steps, dense, tp))
+        llm = LLM(**engine_arguments(model_dir, batches, max(prompts), steps, dense, tp))
         vocab = ARCHITECTURES[arch]["vocab_size"]
         sampling = SamplingParams(max_tokens=steps, ignore_eos=True, temperature=0.0, detokenize=False)
-        g = torch.Generator().manual_seed(20261024)
-        for batch in batches:
-            prompts = [{"prompt_token_ids": torch.randint(0, vocab, (prompt,), generator=g).tolist()} for _ in range(batch)]
-            llm.generate(prompts, sampling, use_tqdm=False)                      # warm-up pass
-            llm.collective_rpc("formal_begin", args=(batch,))
-            llm.generate(prompts, sampling, use_tqdm=False)
-            timing = llm.collective_rpc("formal_end")[0]
-            row = {"arch": arch, "dense": dense, "tp": tp, "batch": batch, "prompt": prompt, "steps": timing["steps"],
-                   "decode_tokens_per_s": batch * timing["steps"] / (timing["decode_span_ms"] * 1e-3),
-                   "decode_ms_per_step": timing["decode_ms_per_step"],
-                   "gpu_ms_per_step": timing["sum_step_gpu_ms"] / timing["steps"],
-                   "context": [timing["context_min"], timing["context_max"]], "graph_steps": timing["graph_steps"]}
-            results.append(row)
-            print(json.dumps(row), flush=True)
+        for prompt in prompts:
+            g = torch.Generator().manual_seed(20261024 + prompt)
+            for batch in batches:
+                ids = [{"prompt_token_ids": torch.randint(0, vocab, (prompt,), generator=g).tolist()} for _ in range(batch)]
+
+                def timed():
+                    llm.collective_rpc("formal_begin", args=(batch,))
+                    llm.generate(ids, sampling, use_tqdm=False)
+                    return llm.collective_rpc("formal_end")[0]
+                for attempt in range(attempts):
+                    llm.generate(ids, sampling, use_tqdm=False)                  # warm-up pass
+                    cell = summarise([timed() for _ in range(samples)], batch)
+                    if cell["cv"] <= cv_gate:
+                        break
+                row = {"arch": arch, "dense": dense, "tp": tp, "batch": batch, "prompt": prompt, "samples": samples,
+                       "attempts": attempt + 1, "stable": cell["cv"] <= cv_gate, **cell,
+                       "decode_ms_per_step": cell["median_ms_per_step"]}
+                results.append(row)
+                print(json.dumps(row), flush=True)
         if not dense:
             audit = llm.collective_rpc("hygemm_model_audit")[0]
             print(json.dumps({"audit_layers": len(audit), "first": audit[0] if audit else None}), flush=True)
     return results
 
 
+def append_table(path, rows, note: str = "") -> None:
+    """Markdown rows `arch | linears | tp | prompt | batch | tokens/s | ms/step | CV | attempts` appended to `path`."""
+    path = Path(path)
+    fresh = not path.exists()
+    with path.open("a") as f:
+        if fresh:
+            f.write("| arch | linears | TP | prompt | batch | decode tokens/s | ms/step (median) | CV | attempts | FULL-graph steps |\n")
+            f.write("|---|---|---|---|---|---|---|---|---|---|\n")
+        for r in rows:
+            f.write(f"| {r['arch']} | {'dense bf16' if r['dense'] else 'hybrid' + note} | {r['tp']} | {r['prompt']} | {r['batch']} | "
+                    f"{r['decode_tokens_per_s']:.0f} | {r['median_ms_per_step']:.3f} | {r['cv']:.3f} | {r['attempts']} | "
+                    f"{r['graph_steps']}/{r['steps']} |\n")
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("--arch", default="qwen2.5-7b", choices=sorted(ARCHITECTURES))
     ap.add_argument("--batch", default="1,16,128")
-    ap.add_argument("--prompt", type=int, default=128)
+    ap.add_argument("--prompt", default="128", help="prompt length, or several separated by commas")
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--layers", type=int, default=None, help="fewer decoder layers (smoke runs)")
     ap.add_argument("--dense", action="store_true")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size (one worker process per GPU)")
+    ap.add_argument("--samples", type=int, default=5, help="timed generations per cell after one warm-up")
+    ap.add_argument("--cv", type=float, default=0.05, help="largest accepted coefficient of variation of a cell")
+    ap.add_argument("--table", default=None, help="append the rows as a markdown table to this file")
     args = ap.parse_args(argv)
-    run(args.arch, [int(b) for b in args.batch.split(",")], args.prompt, args.steps, args.dense, args.layers, args.tp)
+    rows = run(args.arch, [int(b) for b in args.batch.split(",")], [int(v) for v in args.prompt.split(",")], args.steps,
+               args.dense, args.layers, args.tp, args.samples, args.cv)
+    if args.table:
+        fused = os.environ.get("HYGEMM_FUSE_SILU", "0") == "1"
+        append_table(args.table, rows, " + fused SwiGLU producer" if fused and not args.dense else "")
 
 
 if __name__ == "__main__":

@@ -65,3 +65,22 @@ def test_benchmark_shards_cover_the_layer_at_every_world_size():
             assert all(a[1] == b[0] for a, b in zip(pieces, pieces[1:]))
             assert all((e - b) % 128 == 0 and e > b for b, e in pieces)
             assert max(e - b for b, e in pieces) - min(e - b for b, e in pieces) <= 128
+
+
+def test_cell_summary_follows_the_reference_protocol(tmp_path):
+    """Median of the samples, population coefficient of variation, tokens/s = batch * 1000 / median ms
+    (integrations/vllm/formal/benchmark.py:84-89 of the reference), and the markdown row of a cell."""
+    samples = [{"decode_ms_per_step": t, "steps": 127, "graph_steps": 127, "sum_step_gpu_ms": 100.0 * t,
+                "context_min": 128, "context_max": 255} for t in (2.0, 2.2, 2.1, 2.05, 2.15)]
+    cell = decode.summarise(samples, 16)
+    assert cell["median_ms_per_step"] == 2.1 and abs(cell["decode_tokens_per_s"] - 16000 / 2.1) < 1e-9
+    import statistics
+    assert abs(cell["cv"] - statistics.pstdev([2.0, 2.2, 2.1, 2.05, 2.15]) / 2.1) < 1e-12 and cell["cv"] < 0.05
+    assert cell["context"] == [128, 255] and cell["steps"] == 127
+    row = dict(cell, arch="qwen2.5-7b", dense=False, tp=1, batch=16, prompt=128, attempts=1)
+    table = tmp_path / "t.md"
+    decode.append_table(table, [row], " + fused SwiGLU producer")
+    decode.append_table(table, [dict(row, dense=True)])
+    lines = table.read_text().splitlines()
+    assert lines[0].startswith("| arch | linears") and len(lines) == 4
+    assert "hybrid + fused SwiGLU producer" in lines[2] and "dense bf16" in lines[3] and "127/127" in lines[2]
