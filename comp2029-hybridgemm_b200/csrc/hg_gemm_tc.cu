@@ -51,7 +51,6 @@
 #include <mutex>
 
 #include "hg_gemm_tc.cuh"
-#include "hg_tp.cuh"
 
 namespace hg {
 
@@ -101,7 +100,6 @@ struct TcParams {
   float* workspace;
   int* counters;
   int* status;
-  TpExchange tp;   // tp.world > 0: the launch also performs the row-parallel exchange of its result (hg_run_allreduce)
 };
 
 enum : int { kErrProducer = 1, kErrMmaFull = 2, kErrMmaAcc = 3, kErrEpilogue = 4, kErrDrain = 5, kErrLoader = 6 };
@@ -719,33 +717,6 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols) : "memory");
   }
 
-  if (p.tp.world > 0) {
-    // ------------------------------------------------------------------ row-parallel exchange, same launch
-    // Every CTA has stored its part of this rank's partial result into the rank's exchange buffer.  The last
-    // CTA to get here (a ticket; nobody waits for it yet) tells every rank that the partial is complete; then
-    // all CTAs wait, bounded, until every rank has said so, and each adds its share of the result from the
-    // buffers of all ranks, pulled over NVLink.  The grid is at most one CTA per SM and every CTA of it is
-    // resident before the kernel that follows may start, so the wait cannot starve a CTA that it depends on.
-    const int epoch = *reinterpret_cast<const volatile int*>(p.tp.state) + 1;
-    if (threadIdx.x == 0) {
-      __threadfence();   // cumulative over the stores of this CTA's epilogue threads, ordered by the barrier above
-      *ticket_slot = atomicAdd(p.tp.state + 1, 1) == int(gridDim.x) - 1;
-      if (*ticket_slot) p.tp.state[1] = 0;
-    }
-    __syncthreads();
-    if (*ticket_slot) tp_publish(p.tp, epoch, int(threadIdx.x));
-    const int ok = __syncthreads_and(tp_wait(p.tp, epoch, int(threadIdx.x)));
-    tp_sum<T>(p.tp, epoch, ok, int64_t(blockIdx.x) * blockDim.x + threadIdx.x, int64_t(gridDim.x) * blockDim.x);
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      __threadfence();
-      if (atomicAdd(p.tp.state + 3, 1) == int(gridDim.x) - 1) {   // every CTA has read the count by now
-        p.tp.state[3] = 0;
-        __threadfence();
-        *reinterpret_cast<volatile int*>(p.tp.state) = epoch;
-      }
-    }
-  }
 }
 
 // Fixed-order sum of the partial tiles of every cut (tile, token tile) for wide token tiles
@@ -1147,7 +1118,7 @@ static TcParams base_params(const Plan& plan, const hg_problem& l, const hg_prob
 }
 
 void tc_run(TcGemm* g, const hg_problem& l, const hg_problem& h, cudaStream_t stream, const void* x, int x_dtype,
-            const PartialTarget* partial, const TpExchange* exchange) {
+            const PartialTarget* partial) {
   const bool fused = x != nullptr;
   validate(l, h, fused);
   if (fused) {
@@ -1172,11 +1143,6 @@ void tc_run(TcGemm* g, const hg_problem& l, const hg_problem& h, cudaStream_t st
     p.out.parity_bytes = partial->half_bytes;
   } else {
     p.out.ptr = any.output;
-  }
-  if (exchange) {
-    if (!partial) throw std::runtime_error("An exchange needs the partial result in an exchange buffer");
-    if (!tc_exchange_in_launch(g)) throw std::runtime_error("This schedule finishes its tiles in a second launch; exchange separately");
-    p.tp = *exchange;
   }
   p.x = static_cast<const uint16_t*>(x);
   p.x_bf16 = x_dtype == HG_DTYPE_BF16;
@@ -1217,12 +1183,6 @@ void tc_run(TcGemm* g, const hg_problem& l, const hg_problem& h, cudaStream_t st
                     : launch_kernel(hybrid_gemm_tc_kernel<__half, false>, grid, plain, plan.smem_bytes, stream, p, *map_high, *map_act, g->heads);
   check(launched, "hybrid GEMM launch");
   launch_reduce(plan, p, g->d_cut, g->dtype, stream, true);
-}
-
-bool tc_exchange_in_launch(const TcGemm* g) {
-  // Cut tiles of wide token tiles are finished by the separate reduce launch: the partial result is then
-  // only complete after that launch, and the exchange has to be a launch of its own behind it.
-  return !(g->plan.external_reduce && !g->plan.cut_tiles.empty());
 }
 
 void tc_destroy(TcGemm* g) {

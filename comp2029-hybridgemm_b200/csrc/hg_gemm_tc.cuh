@@ -3,7 +3,6 @@
 #include <vector>
 
 #include "hg_common.cuh"
-#include "hg_tp.cuh"
 
 namespace hg {
 
@@ -58,10 +57,7 @@ struct PartialTarget {
   const int* state;    // device word counting finished exchanges
 };
 void tc_run(TcGemm*, const hg_problem& l, const hg_problem& h, cudaStream_t stream, const void* x = nullptr,
-            int x_dtype = HG_DTYPE_BF16, const PartialTarget* partial = nullptr, const TpExchange* exchange = nullptr);
-// `exchange` (optional, with `partial`): the launch also tells the peers, waits for them and adds the partial
-// results of all ranks into exchange->out.  Only for schedules that finish every tile inside the GEMM launch:
-bool tc_exchange_in_launch(const TcGemm*);
+            int x_dtype = HG_DTYPE_BF16, const PartialTarget* partial = nullptr);
 void tc_destroy(TcGemm*);
 const Plan& tc_plan(const TcGemm*);
 void tc_kernel_attributes(int* registers, int* local_bytes);

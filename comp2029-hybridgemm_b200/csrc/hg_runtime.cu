@@ -117,29 +117,6 @@ int hg_run_partial(void* handle, const hg_problem* l, const hg_problem* h, const
   HG_CATCH
 }
 
-int hg_run_allreduce(void* handle, const hg_problem* l, const hg_problem* h, const void* x, int x_dtype,
-                     void* const* buffers, int64_t half_bytes, int f32, int world, int rank, int* const* flags,
-                     int* state, void* out, void* stream) {
-  HG_TRY
-  if (!handle || !l || !h) throw std::runtime_error("Null argument to hg_run_allreduce");
-  auto* r = static_cast<hg::Runner*>(handle);
-  const hg_problem& any = l->rows ? *l : *h;
-  const hg::TpExchange exchange = hg::make_exchange(buffers, out, int64_t(any.tokens) * any.outputs, half_bytes, f32, world,
-                                                    rank, flags, state);
-  const hg::PartialTarget target{buffers[rank], half_bytes, f32, state};
-  auto s = static_cast<cudaStream_t>(stream);
-  if (!hg::same_shape(*l, r->low) || !hg::same_shape(*h, r->high)) throw std::runtime_error("Kernel cannot rebind to a different shape");
-  if (hg::tc_exchange_in_launch(r->tc)) {
-    hg::tc_run(r->tc, *l, *h, s, x, x_dtype, &target, &exchange);      // GEMM and exchange in one launch
-  } else {
-    hg::tc_run(r->tc, *l, *h, s, x, x_dtype, &target);                 // GEMM (+ reduce launch), then the exchange
-    if (hg_tp_allreduce(buffers, out, int64_t(any.tokens) * any.outputs, half_bytes, f32, world, rank, flags, state,
-                        r->dtype, stream))
-      throw std::runtime_error(hg::last_error());
-  }
-  HG_CATCH
-}
-
 int hg_info(void* handle, int* out) {
   HG_TRY
   if (!handle || !out) throw std::runtime_error("Null argument to hg_info");

@@ -154,8 +154,8 @@ int hg_static_status(void* stream, int* status);
  * tensor_parallel_size > 1 (integrations/vllm/hygemm_vllm/quantization.py:81-83).
  *
  * Every rank owns an exchange buffer of 2 x half_bytes and a flag array of `world` ints, both mapped on
- * every peer (CUDA IPC / symmetric memory), plus four private ints of `state` (exchange count, block ticket,
- * status, second block ticket), all zeroed once.  One exchange is two calls on every rank:
+ * every peer (CUDA IPC / symmetric memory), plus three private ints of `state` (exchange count, block ticket,
+ * status), all zeroed once.  One exchange is two calls on every rank:
  *
  *   hg_run_partial   the GEMM of hg_run (or hg_run_x when `x` is not null), whose scatter epilogue stores this
  *                    rank's partial [tokens,outputs] into one half of its OWN buffer: 16-bit elements, or fp32
@@ -177,16 +177,6 @@ int hg_run_partial(void* handle, const hg_problem* low, const hg_problem* high, 
                    void* buffer, int64_t half_bytes, int f32, const int* state, void* stream);
 int hg_tp_allreduce(void* const* buffers, void* out, int64_t elems, int64_t half_bytes, int f32, int world, int rank,
                     int* const* flags, int* state, int dtype, void* stream);
-/* Both halves of an exchange in ONE call and, wherever the schedule finishes every tile inside the GEMM launch
- * (every schedule up to 48 tokens, data-parallel ones above), in ONE launch: each CTA stores its part of the
- * partial result into `buffers[rank]`, the last CTA to finish publishes the flags, every CTA then waits (bounded,
- * as above) for all ranks and adds its share of `out` from the buffers of all ranks.  The exchange then costs no
- * kernel boundary: the sum starts as soon as the slowest rank's last tile is stored.  `state` has four ints
- * (the fourth is the ticket of the summing phase).  Otherwise the call is hg_run_partial followed by
- * hg_tp_allreduce. */
-int hg_run_allreduce(void* handle, const hg_problem* low, const hg_problem* high, const void* x, int x_dtype,
-                     void* const* buffers, int64_t half_bytes, int f32, int world, int rank, int* const* flags,
-                     int* state, void* out, void* stream);
 /* Reads and clears state[2] (0 = every wait was satisfied). */
 int hg_tp_status(int* state, void* stream, int* status);
 

@@ -104,65 +104,6 @@ def test_two_emulated_ranks_sum_bit_exact(tokens, fused, dtype):
     assert all(layer.status()[0] == 0 for layer in layers)
 
 
-@pytest.mark.parametrize("tokens,fused", [(1, True), (8, False), (16, True), (33, False), (128, False)])
-def test_exchange_inside_the_gemm_launch(tokens, fused):
-    """`hg_run_allreduce`: each emulated rank's call finds the other rank's partial already in its buffer
-    (written by hg_run_partial) and that rank's flag already set, so the launch never waits for a later one;
-    the result must be the bits of the two-call path."""
-    world, k, outputs, high, dtype = 2, 1024, 640, 96, torch.bfloat16
-    layers, xs = shards(tokens, k, outputs, high, world, dtype)
-    elems, f32 = tokens * outputs, int(tokens <= 16)
-    half = -(-elems * 4 // 256) * 256
-    bufs, flags = buffers(world, half)
-    ex = [LocalExchange(world, r, half, bufs, flags, dtype) for r in range(world)]
-    lib, stream = native.library(), torch.cuda.current_stream().cuda_stream
-    packed = [native.pack(x) for x in xs]
-    for layer, (q, sf) in zip(layers, packed):
-        layer.run_packed(q, sf)                                            # warms the handles
-    for epoch in (1, 2, 3):
-        # reference: the two-call path on fresh buffers
-        ref_bufs, ref_flags = buffers(world, half)
-        ref = [LocalExchange(world, r, half, ref_bufs, ref_flags, dtype) for r in range(world)]
-        for e in ref:
-            e.state[0] = epoch - 1
-        ref_flags[0][1] = epoch
-        want = [torch.empty(tokens, outputs, dtype=dtype, device="cuda") for _ in range(world)]
-
-        def call_partial(r, target, state):
-            layer, (q, sf) = layers[r], packed[r]
-            low, high_p = layer.problems(xs[r] if fused else q, xs[r] if fused else sf, want[r])
-            handle = layer.handles[next(k_ for k_ in layer.handles if k_[0] == tokens)]
-            native.check(lib.hg_run_partial(handle, C.byref(low), C.byref(high_p), xs[r].data_ptr() if fused else None,
-                                            native.DTYPES[dtype], target.data_ptr(), half, f32, state.data_ptr(), stream))
-        for r in range(world):
-            call_partial(r, ref_bufs[r], ref[r].state)
-        for r in range(world):
-            native.check(lib.hg_tp_allreduce(ref[r].buffer_ptrs, want[r].data_ptr(), elems, half, f32, world, r,
-                                             ref[r].flag_ptrs, ref[r].state.data_ptr(), native.DTYPES[dtype], stream))
-        torch.cuda.synchronize()
-        assert (bits(want[0]) == bits(want[1])).all()
-        # one-call path, rank by rank: the peer's partial and flag are in place before the launch
-        for r in range(world):
-            peer = 1 - r
-            scratch = torch.full((4,), 0, dtype=torch.int32, device="cuda")
-            scratch[0] = epoch - 1
-            call_partial(peer, bufs[peer], scratch)
-            flags[r][peer] = epoch
-            torch.cuda.synchronize()
-            y = torch.full((tokens, outputs), float("nan"), dtype=dtype, device="cuda")
-            layer, (q, sf) = layers[r], packed[r]
-            low, high_p = layer.problems(xs[r] if fused else q, xs[r] if fused else sf, y)
-            handle = layer.handles[next(k_ for k_ in layer.handles if k_[0] == tokens)]
-            native.check(lib.hg_run_allreduce(handle, C.byref(low), C.byref(high_p), xs[r].data_ptr() if fused else None,
-                                              native.DTYPES[dtype], ex[r].buffer_ptrs, half, f32, world, r, ex[r].flag_ptrs,
-                                              ex[r].state.data_ptr(), y.data_ptr(), stream))
-            torch.cuda.synchronize()
-            assert ex[r].status() == 0 and ex[r].state[0].item() == epoch
-            assert ex[r].state[1].item() == 0 and ex[r].state[3].item() == 0          # both tickets re-armed
-            assert (bits(y) == bits(want[0])).all(), (r, epoch)
-    assert all(layer.status()[0] == 0 for layer in layers)
-
-
 def test_single_rank_exchange_equals_plain_run():
     layers, xs = shards(16, 512, 384, 40, 1, torch.bfloat16)
     half = 16 * 384 * 4
@@ -181,7 +122,7 @@ def test_single_rank_exchange_equals_plain_run():
 def test_missing_peer_ends_the_wait_with_a_status(monkeypatch):
     """A flag that nothing sets: the all-reduce gives up after its limit (about a second), reports which rank it
     waited for, fills the output with NaN so the failure cannot pass for a result, still advances the exchange
-    count and the context stays usable; the same for the exchange inside the GEMM launch."""
+    count and the context stays usable; the same through `DualLinear.run_exchange`."""
     world, tokens, outputs = 2, 8, 256
     half = tokens * outputs * 4
     bufs, flags = buffers(world, half)

@@ -213,7 +213,6 @@ def test_exchange_arguments_are_checked():
     assert lib.hg_tp_allreduce(ptrs, 16, 8, 16, 1, 2, 0, ptrs, 16, 1, None) == -1      # 8 fp32 values do not fit 16 bytes
     assert lib.hg_tp_allreduce(ptrs, 16, 8, 16, 0, 9, 0, ptrs, 16, 1, None) == -1
     assert lib.hg_run_partial(None, None, None, None, 0, None, 16, 0, None, None) == -1
-    assert lib.hg_run_allreduce(None, None, None, None, 0, ptrs, 16, 0, 2, 0, ptrs, None, None, None) == -1
 
 
 def test_gemm_arguments_are_checked_on_every_policy():
