@@ -91,6 +91,7 @@ struct TcParams {
   int issuers;    // MMA-issuing threads = independent accumulators per unit (1, 2 or 4)
   int acc_slots;  // accumulator buffers: 2 lets the epilogue of a unit overlap the next main loop
   int external_reduce;  // cut tiles only store partial sums; splitk_reduce_kernel adds them
+  int staged_fixup;     // the last piece of a cut tile sums the pieces from shared memory (bulk copies) when its ring is idle
   const uint8_t* weight_low;
   const uint16_t* x;  // fused mode: 16-bit activations [tokens,k], quantised in the kernel (tokens <= 16); else null
   int x_bf16;
@@ -285,14 +286,15 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
   const SmemLayout lay = smem_layout(p.stages, p.n_tile);
 
-  // Barrier block: full[stages], empty[stages], acc_full[2], acc_empty[2], drain, then three words.
+  // Barrier block: full[stages], empty[stages], acc_full[2], acc_empty[2], drain, fix-up, then three words.
   const uint32_t bars = base + lay.bars;
   auto full_bar = [&](int s) { return bars + uint32_t(s) * 8u; };
   auto empty_bar = [&](int s) { return bars + uint32_t(p.stages + s) * 8u; };
   auto acc_full_bar = [&](int s) { return bars + uint32_t(2 * p.stages + s) * 8u; };
   auto acc_empty_bar = [&](int s) { return bars + uint32_t(2 * p.stages + 2 + s) * 8u; };
   const uint32_t drain_bar = bars + uint32_t(2 * p.stages + 4) * 8u;
-  volatile int* words = reinterpret_cast<volatile int*>(base_ptr + lay.bars + (2 * p.stages + 5) * 8);
+  const uint32_t fix_bar = bars + uint32_t(2 * p.stages + 5) * 8u;   // partial sums of a cut tile landed in shared memory
+  volatile int* words = reinterpret_cast<volatile int*>(base_ptr + lay.bars + (2 * p.stages + 6) * 8);
   volatile int* tmem_slot = words;       // TMEM base address written by tcgen05.alloc
   volatile int* abort_flag = words + 1;  // set by the first role whose wait expired
   volatile int* ticket_slot = words + 2; // split-K arrival ticket broadcast
@@ -326,6 +328,7 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
       mbar_init(acc_empty_bar(s), 4);
     }
     mbar_init(drain_bar, uint32_t(p.issuers));
+    mbar_init(fix_bar, 1);
     *abort_flag = 0;
     *ticket_slot = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -667,7 +670,67 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
         const int ticket = *ticket_slot;
         if (ticket == wu.nsplit - 1) {
           const float* src = p.workspace + int64_t(wu.ws_slot) * (int64_t(p.n_tile) * kTileRows) + row_in_tile;
-          if (row_ok) {
+          // The CTA's last unit: its ring is idle (every stage consumed), so one thread asks for all pieces'
+          // partial tiles with bulk copies into it, every byte in flight at once, and the 128 threads add them
+          // from shared memory in K order: one memory round trip per batch of columns, and one batch unless
+          // the pieces are many and the tile wide.
+          const int cols = min(p.n_tile, p.tokens - token0);
+          const int batch = min(cols, int((uint32_t(p.stages) * 32768u) / (uint32_t(wu.nsplit) * 512u)));
+          // Measured (B200, cold graph burst): above 16 tokens the staged sum wins (o_proj at 32 tokens 14.4 ->
+          // 13.8 us, qkv 13.8 -> 12.4, down 19.1 -> 18.2); up to 16 tokens the register path below needs one or
+          // two rounds anyway and the extra fence, barrier and copy issue cost 0.2-0.4 us, so it keeps that path.
+          if (p.staged_fixup && cols > 16 && u + 1 == unit_end && batch > 0) {
+            const float* piece0 = src - row_in_tile;
+            uint32_t fix_phase = 0;
+            for (int cbase = 0; cbase < cols && !error; cbase += batch) {
+              const int nc = min(batch, cols - cbase);
+              if (threadIdx.x == 64) {
+                // the other pieces were written through the generic proxy and acquired by the ticket above;
+                // the bulk copies read them through the async proxy
+                asm volatile("fence.proxy.async;" ::: "memory");
+                mbar_expect_tx(fix_bar, uint32_t(wu.nsplit * nc) * 512u);
+                for (int s = 0; s < wu.nsplit; ++s)
+                  bulk_load(base + lay.a + uint32_t(s * nc) * 512u,
+                            piece0 + (int64_t(s) * p.n_tile + cbase) * kTileRows, uint32_t(nc) * 512u, fix_bar);
+              }
+              const bool landed = mbar_wait(fix_bar, fix_phase, abort_flag);
+              fix_phase ^= 1u;
+              if (!epilogue_all(landed)) { error = kErrEpilogue; break; }
+              if (row_ok) {
+                // four columns x four pieces per round: sixteen independent shared-memory loads in flight,
+                // additions in K order
+                const uint32_t piece_stride = uint32_t(nc) * 512u;
+                const uint32_t row_addr = base + lay.a + uint32_t(row_in_tile) * 4u;
+                for (int c = 0; c < nc; c += 4) {
+                  float sum[4] = {0.f, 0.f, 0.f, 0.f};
+                  for (int s0 = 0; s0 < wu.nsplit; s0 += 4) {
+                    float v[4][4];
+#pragma unroll
+                    for (int ds = 0; ds < 4; ++ds)
+#pragma unroll
+                      for (int j = 0; j < 4; ++j) {
+                        v[ds][j] = 0.f;
+                        if (s0 + ds < wu.nsplit && c + j < nc)
+                          asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v[ds][j])
+                                       : "r"(row_addr + uint32_t(s0 + ds) * piece_stride + uint32_t(c + j) * 512u));
+                      }
+#pragma unroll
+                    for (int ds = 0; ds < 4; ++ds)
+                      if (s0 + ds < wu.nsplit) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) sum[j] += v[ds][j];
+                      }
+                  }
+#pragma unroll
+                  for (int j = 0; j < 4; ++j)
+                    if (c + j < nc)
+                      scatter_store<T>(p.out, out, int64_t(token0 + cbase + c + j) * p.outputs + channel, sum[j]);
+                }
+              }
+              if (cbase + batch < cols) epilogue_sync();   // everyone has read this batch before the next one lands
+            }
+            if (error) break;
+          } else if (row_ok) {
             // Eight columns x four pieces per round: all loads of a round are in flight together (each is an
             // L2 round trip), the additions keep K order.  Columns beyond the token count are not read.
             for (int c = 0; c < p.n_tile && token0 + c < p.tokens; c += 8) {
@@ -763,6 +826,11 @@ splitk_reduce_kernel(const ReduceParams rp) {
 // ---------------------------------------------------------------------------------------------
 
 static int round_up(int v, int m) { return (v + m - 1) / m * m; }
+// HYGEMM_TC_STAGED_FIXUP=0: the last piece of a cut tile always sums the pieces with loads from global memory.
+static bool staged_fixup() {
+  static const bool value = [] { const char* t = std::getenv("HYGEMM_TC_STAGED_FIXUP"); return !(t && t[0] == '0'); }();
+  return value;
+}
 constexpr int kMaxDynamicSmem = 232448;  // 227 KiB, the per-CTA limit of sm_100
 
 Plan make_plan(int rows_low, int rows_high, int tokens, int k, int sms, int schedule) {
@@ -1113,6 +1181,7 @@ static TcParams base_params(const Plan& plan, const hg_problem& l, const hg_prob
   p.issuers = plan.issuers;
   p.acc_slots = plan.acc_slots;
   p.external_reduce = plan.external_reduce ? 1 : 0;
+  p.staged_fixup = staged_fixup() ? 1 : 0;
   p.weight_low = static_cast<const uint8_t*>(l.weight);
   return p;
 }
