@@ -570,6 +570,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--step-only", action="store_true",
+                    help="skip the hot per-shape rows and the prefill rows (launch-list captures of the step itself)")
     ap.add_argument("--gemm", default=None, metavar="NAME:M[:SCHEDULE[:HIGH_FRACTION[:fused]]]",
                     help="profiling aid: run only this GEMM (e.g. gate_up:16) a few times on cold weights and exit")
     ap.add_argument("--quant", default=None, metavar="act|silu:ROWS:K",
@@ -739,7 +741,7 @@ def main():
     hot = {}
     try:
         from hygemm_vllm import native as _native
-        for m in M_SWEEP:
+        for m in ([] if args.step_only else M_SWEEP):
             x = sweep.dev[m]
             gate_up_out = layers[0]["gate_up"].run_packed(*_native.pack(x["x_gate"]))
             packed = {"qkv": _native.pack(x["x_qkv"]), "o_proj": _native.pack(x["x_o"]), "gate_up": _native.pack(x["x_gate"]),
@@ -770,7 +772,7 @@ def main():
     # ---- prefill buckets (the reference's plans reach 2048 tokens): the same kernel in rows of 128-token
     # tiles, the two weight sets alternating so the weights come from HBM; outside the step and its metric.
     prefill = []
-    if world == 1:
+    if world == 1 and not args.step_only:
         try:
             from hygemm_vllm import native as _native
             g2 = torch.Generator().manual_seed(SEED + 7)
