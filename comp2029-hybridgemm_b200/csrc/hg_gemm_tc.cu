@@ -187,10 +187,17 @@ __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
       : "memory");
 }
-__device__ __forceinline__ void tc_load8(uint32_t taddr, uint32_t (&r)[8]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+__device__ __forceinline__ void tc_load16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
                : "r"(taddr));
+}
+// A register filled by a tcgen05.ld issued before the last tc_wait_ld(): passing it through this (empty)
+// volatile statement keeps every use behind that wait, however far ahead the load was issued.
+__device__ __forceinline__ uint32_t tc_loaded(uint32_t v) {
+  asm volatile("" : "+r"(v));
+  return v;
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
@@ -593,6 +600,7 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
     uint32_t ring = 0;
     pdl_wait();  // nothing is written to global memory before every earlier kernel has finished
     char* const out = out_base(p.out);
+    const bool out_f32 = p.out.f32 != 0;
     for (int u = unit_begin; u < unit_end; ++u, ++acc_it) {
       const WorkUnit wu = u == unit_begin ? first_unit : p.units[u];
       const int part = wu.tile >= p.tiles[0];
@@ -615,39 +623,66 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
       float* ws = wu.nsplit > 1
                       ? p.workspace + (int64_t(wu.ws_slot) + wu.split) * (int64_t(p.n_tile) * kTileRows) + row_in_tile
                       : nullptr;
-      for (int c0 = 0; c0 < p.n_tile; c0 += 16) {
-        float r[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) r[i] = 0.f;
-        for (int a = 0; a < p.issuers; ++a) {   // add the issuers' accumulators in a fixed order
-          if (!((owners >> a) & 1u)) continue;
-          uint32_t e[16];
-          tc_load8(taddr + uint32_t(a) * acc_cols + uint32_t(c0), *reinterpret_cast<uint32_t(*)[8]>(&e[0]));
-          tc_load8(taddr + uint32_t(a) * acc_cols + uint32_t(c0 + 8), *reinterpret_cast<uint32_t(*)[8]>(&e[8]));
-          tc_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 16; ++i) r[i] += __uint_as_float(e[i]);
-        }
+      // Sixteen columns (tokens) of this thread's row: to the split-K workspace, or scattered to the output.
+      // The row stride and the number of valid tokens live in registers: the sixteen addresses are one running sum.
+      const int64_t row_stride = p.outputs;
+      const int tokens_left = p.tokens - token0;
+      auto emit = [&](int c0, const float (&r)[16]) {
+        const int valid = tokens_left - c0;
         if (ws) {
 #pragma unroll
           for (int i = 0; i < 16; ++i)
-            if (token0 + c0 + i < p.tokens) ws[int64_t(c0 + i) * kTileRows] = r[i];   // columns nobody will read are skipped
+            if (i < valid) ws[int64_t(c0 + i) * kTileRows] = r[i];   // columns nobody will read are skipped
         } else if (row_ok) {
-          if (!p.out.f32) {
-            uint16_t* column = reinterpret_cast<uint16_t*>(out) + channel;
+          if (!out_f32) {
+            uint16_t* at = reinterpret_cast<uint16_t*>(out) + channel + int64_t(token0 + c0) * row_stride;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const int token = token0 + c0 + i;
-              if (token < p.tokens) column[int64_t(token) * p.outputs] = from_float<T>(r[i]);
-            }
+            for (int i = 0; i < 16; ++i, at += row_stride)
+              if (i < valid) *at = from_float<T>(r[i]);
           } else {
-            float* column = reinterpret_cast<float*>(out) + channel;
+            float* at = reinterpret_cast<float*>(out) + channel + int64_t(token0 + c0) * row_stride;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const int token = token0 + c0 + i;
-              if (token < p.tokens) column[int64_t(token) * p.outputs] = r[i];
-            }
+            for (int i = 0; i < 16; ++i, at += row_stride)
+              if (i < valid) *at = r[i];
           }
+        }
+      };
+      if (!FUSED && p.issuers <= 2 && p.n_tile > 16) {
+        // Wide tiles: the TMEM read of the next sixteen columns is in flight while the current sixteen are
+        // stored.  The issuers' accumulators are added in the same fixed order as below.
+        const bool own0 = owners & 1u, own1 = (owners >> 1) & 1u;
+        uint32_t a[16], b[16];
+        auto fetch = [&](int c0) {
+          if (own0) tc_load16(taddr + uint32_t(c0), a);
+          if (own1) tc_load16(taddr + acc_cols + uint32_t(c0), b);
+        };
+        fetch(0);
+        for (int c0 = 0; c0 < p.n_tile; c0 += 16) {
+          tc_wait_ld();
+          float r[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            r[i] = 0.f;
+            if (own0) r[i] += __uint_as_float(tc_loaded(a[i]));
+            if (own1) r[i] += __uint_as_float(tc_loaded(b[i]));
+          }
+          if (c0 + 16 < p.n_tile) fetch(c0 + 16);
+          emit(c0, r);
+        }
+      } else {
+        for (int c0 = 0; c0 < p.n_tile; c0 += 16) {
+          float r[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) r[i] = 0.f;
+          for (int a = 0; a < p.issuers; ++a) {   // add the issuers' accumulators in a fixed order
+            if (!((owners >> a) & 1u)) continue;
+            uint32_t e[16];
+            tc_load16(taddr + uint32_t(a) * acc_cols + uint32_t(c0), e);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) r[i] += __uint_as_float(e[i]);
+          }
+          emit(c0, r);
         }
       }
       // Accumulator buffer may be overwritten by the next-but-one unit.
@@ -898,7 +933,10 @@ Plan make_plan(int rows_low, int rows_high, int tokens, int k, int sms, int sche
     plan.units.clear();
     plan.cta_begin.assign(1, 0);
     for (auto& list : per) {
-      std::sort(list.begin(), list.end());
+      // Costlier units first, then by position.  An MXFP8 tile scatters its outputs to channels all over the
+      // row (one sector per element); run first, that epilogue hides under the next unit's main loop instead
+      // of ending the CTA.
+      std::sort(list.begin(), list.end(), [&](int a, int b) { return cost[a] != cost[b] ? cost[a] > cost[b] : a < b; });
       for (int i : list) plan.units.push_back(units[i]);
       plan.cta_begin.push_back(int(plan.units.size()));
     }
