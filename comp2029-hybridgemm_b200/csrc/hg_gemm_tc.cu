@@ -90,6 +90,7 @@ struct TcParams {
   int n_tile, stages, dtype;
   int issuers;    // MMA-issuing threads = independent accumulators per unit (1, 2 or 4)
   int acc_slots;  // accumulator buffers: 2 lets the epilogue of a unit overlap the next main loop
+  int split_blocks;  // 1: both issuers consume every stage, issuer q its K128 block q (wide token tiles)
   int external_reduce;  // cut tiles only store partial sums; splitk_reduce_kernel adds them
   int staged_fixup;     // the last piece of a cut tile sums the pieces from shared memory (bulk copies) when its ring is idle
   const uint8_t* weight_low;
@@ -328,7 +329,7 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
     for (int s = 0; s < p.stages; ++s) {
       // TMA thread (with the byte count) + every loader thread (+ every quantiser thread in fused mode)
       mbar_init(full_bar(s), 1 + kLoaderThreads + (FUSED ? kQuantThreads : 0));
-      mbar_init(empty_bar(s), 1);                  // released by the MMA thread's commit
+      mbar_init(empty_bar(s), p.split_blocks ? 2 : 1);   // released by the commit of every issuer that reads the stage
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(acc_full_bar(s), uint32_t(p.issuers));
@@ -526,9 +527,9 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
     // ------------------------------------------------------------------ MMA issuers (warps 1, 10, 11, 12)
     // A tcgen05 instruction costs its issuing thread on the order of a hundred cycles (descriptor set-up
     // through the uniform datapath) whatever its shape, far more than a 128 x n_tile x 32 MMA occupies the
-    // tensor core.  So up to four threads in four warps issue independent streams: issuer q takes pipeline
-    // every I-th pipeline stage and accumulates into its own TMEM accumulator; the epilogue adds the
-    // accumulators in a fixed order, which keeps the result deterministic.
+    // tensor core.  So up to four threads in four warps issue independent streams: issuer q takes every I-th
+    // pipeline stage (or, with split_blocks, its K128 block of every stage) and accumulates into its own TMEM
+    // accumulator; the epilogue adds the accumulators in a fixed order, which keeps the result deterministic.
     const int q = warp == 1 ? 0 : warp - 9;
     if (lane == 0 && q < p.issuers) {
       uint32_t issued = 0;
@@ -556,7 +557,7 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
         // The ring depth is a multiple of the issuer count (1, 2 or 4), so (g % stages) % issuers is g % issuers.
         bool fresh = true;   // this issuer's accumulator has not been written in this unit yet
         for (uint32_t l = 0; l < unit_stages && !error; ++l, ring_slot = ring_slot + 1 == p.stages ? (ring_round ^= 1u, 0) : ring_slot + 1) {
-          if (((ring + l) & issuer_mask) != uint32_t(q)) continue;
+          if (!p.split_blocks && ((ring + l) & issuer_mask) != uint32_t(q)) continue;
           const int kb = wu.kb_begin + 2 * int(l);
           const int nkb = min(2, wu.kb_end - kb);
           const int stage = ring_slot;   // (ring + l) % stages, kept incrementally with its round parity
@@ -566,6 +567,7 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           tc_fence_after();
           for (int i = 0; i < nkb; ++i) {
+            if (p.split_blocks && i != q) continue;
             const uint32_t sf_set = sf_base + (sf_flip ^= 1u) * 8u;
             tc_cp_scales(sf_set, smem_desc(base + lay.sfa + uint32_t(stage) * 1024u + uint32_t(i) * 512u, 0, 128, kSwizzleNone));
             tc_cp_scales(sf_set + 4, smem_desc(base + lay.sfb + uint32_t(stage) * 1024u + uint32_t(i) * 512u, 0, 128, kSwizzleNone));
@@ -575,12 +577,14 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
             for (uint32_t j = 0; j < 4; ++j) {
               // 32 K-elements = 32 bytes further along the swizzled row: start address field += 2.
               tc_mma(tmem_d, desc_a + 2 * j, desc_b + 2 * j, idesc | (j << 29) | (j << 4),
-                     (!fresh || i > 0 || j > 0) ? 1u : 0u, sf_set, sf_set + 4 + sfb_col);
+                     (!fresh || j > 0) ? 1u : 0u, sf_set, sf_set + 4 + sfb_col);
             }
+            fresh = false;
             ++issued;
           }
-          tc_commit(empty_bar(stage));
-          fresh = false;
+          // A stage whose second block lies beyond the unit gives the second issuer nothing to read.
+          if (p.split_blocks && q >= nkb) mbar_arrive(empty_bar(stage));
+          else tc_commit(empty_bar(stage));
         }
         ring += unit_stages;
         // Every issuer reports, also one that had no stage in this unit (its accumulator is then skipped).
@@ -616,8 +620,10 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
       // Issuers that owned a stage of this unit (global stages ring .. ring + unit_stages - 1, by ring slot).
       const uint32_t unit_stages = uint32_t(wu.kb_end - wu.kb_begin + 1) >> 1;
       uint32_t owners = 0;
-      for (uint32_t l = 0; l < unit_stages && l < uint32_t(p.issuers); ++l)
-        owners |= 1u << ((ring + l) & (uint32_t(p.issuers) - 1u));
+      if (p.split_blocks) owners = wu.kb_end - wu.kb_begin >= 2 ? 3u : 1u;
+      else
+        for (uint32_t l = 0; l < unit_stages && l < uint32_t(p.issuers); ++l)
+          owners |= 1u << ((ring + l) & (uint32_t(p.issuers) - 1u));
       ring += unit_stages;
       const uint32_t taddr = tmem_base + lane_addr + uint32_t(slot) * acc_stride;
       float* ws = wu.nsplit > 1
@@ -893,17 +899,26 @@ Plan make_plan(int rows_low, int rows_high, int tokens, int k, int sms, int sche
   if (const char* cap = std::getenv("HYGEMM_TC_STAGES"))  // tuning aid: cap the pipeline depth
     plan.stages = std::max(2, std::min(plan.stages, std::atoi(cap)));
   plan.smem_bytes = 1024 + plan.stages * stage_bytes + kBarrierBytes;
-  // MMA-issuing threads: two up to n_tile = 64, where TMEM (512 columns) holds two double-buffered
-  // accumulators per issuer.  At n_tile = 128 a second issuer would force single-buffered accumulators
-  // and a two-stage ring, which measured slower (gate_up M=128: 40.5 vs 34.3 us), so one issuer there.
-  // The pipeline depth is kept a multiple of the issuer count so the issuers own equally many ring slots
-  // (five stages shared 3:2 measured slower than four shared 2:2).
+  // MMA-issuing threads: two.  Up to n_tile = 64 they own alternate stages and TMEM (512 columns) holds two
+  // double-buffered accumulators per issuer; the pipeline depth is then kept a multiple of the issuer count
+  // so that the issuers own equally many ring slots and each stage barrier has one consumer (five stages
+  // shared 3:2 measured slower than four shared 2:2).
   plan.issuers = plan.n_tile <= 64 ? 2 : 1;
   if (const char* cap = std::getenv("HYGEMM_TC_ISSUERS"))  // tuning aid: 1, 2 or 4
     plan.issuers = std::max(1, std::min(plan.n_tile <= 32 ? 4 : plan.n_tile <= 64 ? 2 : 2, std::atoi(cap)));
   if (plan.issuers == 3) plan.issuers = 2;
+  // Wider tiles have a three-stage ring, so the two issuers share EVERY stage instead, issuer q taking its K128
+  // block q: each stage barrier keeps both consumers in every round, so the depth need not be a multiple of
+  // the issuer count.  At n_tile = 128 TMEM then holds one accumulator per issuer (the epilogue is no longer
+  // overlapped); the halved issue time per stage outweighs that (gate_up at 128 tokens 32.6 -> 30.6 us, at 96
+  // tokens, where two accumulator slots still fit, 30.5 -> 25.6 us).
+  plan.split_blocks = 0;
+  if (plan.n_tile > 64 && plan.issuers == 1) {
+    const char* off = std::getenv("HYGEMM_TC_SPLIT_BLOCKS");   // tuning aid: 0 keeps the single issuer
+    if (!off || std::atoi(off) != 0) { plan.split_blocks = 1; plan.issuers = 2; }
+  }
   plan.acc_slots = plan.issuers * 2 * round_up(plan.n_tile, 32) + plan.issuers * 8 * kScaleSets <= 512 ? 2 : 1;
-  plan.stages = std::max(plan.issuers, plan.stages / plan.issuers * plan.issuers);
+  if (!plan.split_blocks) plan.stages = std::max(plan.issuers, plan.stages / plan.issuers * plan.issuers);
   plan.smem_bytes = 1024 + plan.stages * stage_bytes + kBarrierBytes;
   int cols = plan.issuers * (plan.acc_slots * round_up(plan.n_tile, 32) + 8 * kScaleSets), pow2 = 32;
   while (pow2 < cols) pow2 *= 2;
@@ -1218,6 +1233,7 @@ static TcParams base_params(const Plan& plan, const hg_problem& l, const hg_prob
   p.n_tile = plan.n_tile; p.stages = plan.stages; p.dtype = dtype; p.tmem_cols = uint32_t(plan.tmem_cols);
   p.issuers = plan.issuers;
   p.acc_slots = plan.acc_slots;
+  p.split_blocks = plan.split_blocks;
   p.external_reduce = plan.external_reduce ? 1 : 0;
   p.staged_fixup = staged_fixup() ? 1 : 0;
   p.weight_low = static_cast<const uint8_t*>(l.weight);

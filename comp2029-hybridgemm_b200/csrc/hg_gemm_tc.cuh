@@ -32,6 +32,7 @@ struct Plan {
   int tmem_cols = 0;
   int issuers = 1;         // MMA-issuing threads, each with its own TMEM accumulator
   int acc_slots = 2;       // accumulator buffers per issuer
+  int split_blocks = 0;    // both issuers read every stage, one K128 block each (token tiles wider than 64)
   int ws_slots = 0;        // fp32 [n_tile][128] slots
   int counters = 0;
   bool external_reduce = false;  // cut tiles are summed by splitk_reduce_kernel instead of the last arriver

@@ -74,7 +74,10 @@ def test_every_schedule_covers_each_tile_and_k_block_exactly_once(schedule, toke
         for sms in (148, 7):
             header, units = plan(lo, hi, tokens, k, schedule, sms)
             sched, grid, n_tile, token_tiles, stages, smem, tmem, slots, counters, n_units, reduce2, issuers = header
-            assert reduce2 == int(n_tile >= 64 and slots > 0) and stages % issuers == 0
+            assert reduce2 == int(n_tile >= 64 and slots > 0)
+            # up to 64 tokens the issuers own alternate stages (depth a multiple of their count); wider tiles
+            # have two issuers that both read every stage, one K128 block each, so any depth works
+            assert (issuers == 2 and stages >= 2) if n_tile > 64 else stages % issuers == 0
             assert 1 <= grid <= sms and n_tile % 16 == 0 and 16 <= n_tile <= 128
             # several token tiles only with 128-token tiles, or two 64-token tiles for 65..128 tokens on a
             # layer with few row tiles (the activation scale columns of a tile start on an even TMEM column)
