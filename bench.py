@@ -68,9 +68,10 @@ def gemm_bytes(m, k, n, h):
 
 # dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of the same launch, from the ncu
 # captures summarised under profiles/ (one per shape class; cold weights, weight copies cycled).  The ratio
-# does not move with the token count inside a class: the weights are read once and dominate.
+# does not move with the token count inside a class: the weights are read once and dominate.  Above 32 tokens
+# part of the output is still in L2 when the launch ends (gate_up at 128 tokens: 9.7 MB written, 3.8 MB reach DRAM).
 DRAM_TRAFFIC_RATIO = {("gate_up", "decode"): 1.01, ("down", "decode"): 1.00, ("qkv", "decode"): 0.99,
-                      ("o_proj", "decode"): 0.99, ("gate_up", "wide"): 1.01, ("down", "wide"): 1.00,
+                      ("o_proj", "decode"): 0.99, ("gate_up", "wide"): 0.93, ("down", "wide"): 0.98,
                       ("qkv", "wide"): 0.99, ("o_proj", "wide"): 0.99}
 
 
