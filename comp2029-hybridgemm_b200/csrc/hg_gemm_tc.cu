@@ -913,10 +913,10 @@ Plan make_plan(int rows_low, int rows_high, int tokens, int k, int sms, int sche
   // overlapped); the halved issue time per stage outweighs that (gate_up at 128 tokens 32.6 -> 30.6 us, at 96
   // tokens, where two accumulator slots still fit, 30.5 -> 25.6 us).
   plan.split_blocks = 0;
-  if (plan.n_tile > 64 && plan.issuers == 1) {
-    const char* off = std::getenv("HYGEMM_TC_SPLIT_BLOCKS");   // tuning aid: 0 keeps the single issuer
-    if (!off || std::atoi(off) != 0) { plan.split_blocks = 1; plan.issuers = 2; }
-  }
+  const char* split_text = std::getenv("HYGEMM_TC_SPLIT_BLOCKS");   // tuning aid: 0 never, 1 above 64 tokens, 2 always
+  const int split_mode = split_text ? std::atoi(split_text) : 1;
+  if (plan.n_tile > 64 && plan.issuers == 1 && split_mode != 0) { plan.split_blocks = 1; plan.issuers = 2; }
+  else if (plan.issuers == 2 && split_mode == 2) plan.split_blocks = 1;
   plan.acc_slots = plan.issuers * 2 * round_up(plan.n_tile, 32) + plan.issuers * 8 * kScaleSets <= 512 ? 2 : 1;
   if (!plan.split_blocks) plan.stages = std::max(plan.issuers, plan.stages / plan.issuers * plan.issuers);
   plan.smem_bytes = 1024 + plan.stages * stage_bytes + kBarrierBytes;
