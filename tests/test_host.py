@@ -67,6 +67,21 @@ SHAPES = [(4096, 512, 3584), (3200, 384, 3584), (34048, 3840, 3584), (3200, 384,
           (257, 0, 256), (0, 257, 256), (1, 1, 128), (129, 127, 384)]
 
 
+def test_data_parallel_ctas_run_their_mxfp8_tiles_first():
+    """An MXFP8 tile scatters to channels all over the output row; first in its CTA, that epilogue runs under
+    the next unit's main loop instead of ending the CTA."""
+    lo, hi, k = 34048, 3840, 3584
+    tiles_low = lo // 128
+    for tokens in (16, 128, 300):
+        header, units = plan(lo, hi, tokens, k, schedule=1)
+        per_cta = {}
+        for cta, tile, *_ in units:
+            per_cta.setdefault(int(cta), []).append(int(tile) >= tiles_low)
+        assert any(any(flags) for flags in per_cta.values())
+        for flags in per_cta.values():
+            assert flags == sorted(flags, reverse=True)     # every MXFP8 unit precedes every MXFP4 unit
+
+
 @pytest.mark.parametrize("schedule", [0, 1, 2, 3])
 @pytest.mark.parametrize("tokens", [1, 16, 17, 128, 130, 300])
 def test_every_schedule_covers_each_tile_and_k_block_exactly_once(schedule, tokens):
