@@ -20,11 +20,12 @@
 // * Scales: the 512-byte atoms (128 rows x 4 K32 groups) go to TMEM with
 //   tcgen05.cp 32x128b.warpx4; the byte of the current K32 block is selected
 //   with the a_sf_id/b_sf_id descriptor fields.
-// * Issue: up to four MMA-issuing threads in separate warps (two by default up
-//   to 64-token tiles, one at 128), each owning every I-th pipeline stage and
-//   its own accumulator: a tcgen05 instruction costs its issuing thread 50-430
-//   cycles whatever its shape (MMA 90, scale copy 51, commit 432) and threads
-//   issue in parallel.
+// * Issue: up to four MMA-issuing threads in separate warps (two by default),
+//   each with its own accumulator: a tcgen05 instruction costs its issuing
+//   thread 50-430 cycles whatever its shape (MMA 90, scale copy 51, commit 432)
+//   and threads issue in parallel.  Up to 64-token tiles issuer q owns every
+//   I-th pipeline stage; wider tiles have a three-stage ring, and there both
+//   issuers read every stage, issuer q its K128 block q.
 // * Decode sizes (at most 16 tokens) can quantise their activations in the
 //   launch: the FUSED instantiation adds four quantiser warps (hg_run_x).
 // * Row-parallel tensor parallelism: the epilogue can store the partial result
@@ -36,10 +37,14 @@
 //   partials to a workspace; up to 48-token tiles the LAST unit to arrive
 //   (one acq_rel ticket, no spinning) sums the partials in K order, wider
 //   tiles are summed by splitk_reduce_kernel; either way deterministic.
-// * Epilogue: tcgen05.ld 32x32b, accumulators added in a fixed order, fp32 ->
-//   bf16/fp16 (RNE), scattered straight to out[t*N + ids[r]]; consecutive lanes
-//   own consecutive rows, so sorted maps give contiguous 64-byte runs.  Two
-//   accumulator slots let the epilogue of one unit overlap the next main loop.
+// * Epilogue: tcgen05.ld 32x32b.x16 (the next sixteen columns in flight while
+//   the current ones are stored), accumulators added in a fixed order, fp32 ->
+//   bf16/fp16 (RNE), scattered straight to out[t*N + ids[r]] along one running
+//   address per sixteen tokens; consecutive lanes own consecutive rows, so
+//   sorted maps give contiguous 64-byte runs.  Two accumulator slots (where
+//   TMEM holds them: up to 96-token tiles) let the epilogue of one unit overlap
+//   the next main loop; MXFP8 tiles, whose stores scatter over the whole row,
+//   run first in their CTA for the same reason.
 // * Every mbarrier wait is bounded; on expiry the CTA records a code in the
 //   status word, lets copies in flight land, frees TMEM and exits.
 #include <cuda.h>
