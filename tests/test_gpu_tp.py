@@ -1,6 +1,6 @@
 """Row-parallel exchange (hg_run_partial + hg_tp_allreduce) on ONE GPU.
 
-Two ranks are emulated by two sets of buffers in the same device memory and launches in an order in
+Ranks (two, and once eight) are emulated by one set of buffers each in the same device memory and launches in an order in
 which no launch ever waits for a later one: both GEMMs write their partials first, the flag the first
 all-reduce would wait for is written by the host beforehand (standing in for the other rank's publish), and
 the second all-reduce finds the first one's publish already there.  The sum must equal the fp32 sum of the
@@ -54,7 +54,18 @@ def buffers(world, half_bytes):
 @pytest.mark.parametrize("tokens,fused", [(1, True), (16, True), (16, False), (48, False), (100, False), (128, False), (130, False)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_two_emulated_ranks_sum_bit_exact(tokens, fused, dtype):
-    world, k, outputs, high = 2, 1024, 640, 96
+    emulated_ranks_sum_bit_exact(2, tokens, fused, dtype)
+
+
+@pytest.mark.parametrize("tokens,fused", [(16, True), (128, False)])
+def test_eight_emulated_ranks_sum_bit_exact(tokens, fused):
+    """The widest world the exchange takes: rank r's all-reduce finds the flags of the ranks before it published by
+    their kernels and those of the ranks after it written by the host ahead of time."""
+    emulated_ranks_sum_bit_exact(8, tokens, fused, torch.bfloat16)
+
+
+def emulated_ranks_sum_bit_exact(world, tokens, fused, dtype):
+    k, outputs, high = 1024, 640, 96
     layers, xs = shards(tokens, k, outputs, high, world, dtype)
     elems = tokens * outputs
     f32 = int(tokens <= 16)
@@ -78,11 +89,18 @@ def test_two_emulated_ranks_sum_bit_exact(tokens, fused, dtype):
                 native.check(lib.hg_run_partial(handle, C.byref(low), C.byref(high_p), None, 0, out32.data_ptr(), half, 1,
                                                 st.data_ptr(), stream))
                 partial32.append(out32[half:half + elems * 4].view(torch.float32).clone())   # exchange 1 -> second half
-            want = (partial32[0] + partial32[1]).to(dtype).view(tokens, outputs)
+            total = partial32[0]
+            for r in range(1, world):             # rank order, as the kernel adds
+                total = total + partial32[r]
+            want = total.to(dtype).view(tokens, outputs)
         else:
             partial = [layers[r].run_packed(*packed[r]) for r in range(world)]
-            want = (partial[0].float() + partial[1].float()).to(dtype)
-        flags[0][1] = epoch                       # rank 1's publish, ahead of time
+            total = partial[0].float()
+            for r in range(1, world):
+                total = total + partial[r].float()
+            want = total.to(dtype)
+        for r in range(world):                    # the publishes of the ranks that run later, ahead of time
+            flags[r][r + 1:world] = epoch
         ys = [torch.empty(tokens, outputs, dtype=dtype, device="cuda") for _ in range(world)]
         for r in range(world):                    # both GEMMs write their partials before any all-reduce runs
             layer, (q, sf) = layers[r], packed[r]
