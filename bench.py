@@ -489,10 +489,43 @@ def run_single_gemm(args, device):
     seconds = statistics.median(times)
     nbytes = gemm_bytes(m, k, n, h)
     info = layers[0].info(m)
-    print(json.dumps({"gemm": name, "M": m, "K": k, "N": n, "H": h, "schedule": info[0], "n_tile": info[2],
-                      "stages": info[4], "copies": copies, "us_median": seconds * 1e6, "us_min": min(times) * 1e6,
-                      "GBps": nbytes / seconds / 1e9, "algorithmic_bytes": nbytes,
-                      "status": [layer.status() for layer in layers][:2]}))
+    line = {"gemm": name, "M": m, "K": k, "N": n, "H": h, "schedule": info[0], "n_tile": info[2],
+            "stages": info[4], "copies": copies, "us_median": seconds * 1e6, "us_min": min(times) * 1e6,
+            "GBps": nbytes / seconds / 1e9, "algorithmic_bytes": nbytes,
+            "status": [layer.status() for layer in layers][:2]}
+    if args.timeline:
+        line["timeline"] = cta_timeline(lib, [c[0] for c in calls], stream)
+    print(json.dumps(line))
+
+
+TIMELINE_POINTS = ["entry", "setup_done", "wait_released", "first_full_stage", "unit0_committed", "unit1_committed",
+                   "unit2_committed", "unit3_committed", "epilogue0_start", "epilogue0_end", "epilogue1_start",
+                   "epilogue1_end", "epilogue2_start", "epilogue2_end"]
+
+
+def cta_timeline(lib, handles, stream):
+    """Per-CTA time stamps of the last launch of each handle (trace build of the library): for the launch that ran
+    last, microseconds after its first CTA entered, as [min, median, 90th percentile, max] over the grid per point,
+    and the distance to the first entry of the launch before it.  The global timer ticks in steps of up to 0.5 us."""
+    import ctypes as C
+    import numpy as np
+    traces = []
+    for handle in handles:
+        buf = (C.c_uint64 * (16 * 1024))()
+        count = C.c_int(0)
+        from hygemm_vllm import native
+        native.check(lib.hg_trace(handle, stream, buf, len(buf), C.byref(count)))
+        traces.append(np.frombuffer(buf, dtype=np.uint64, count=count.value).reshape(-1, 16).astype(np.int64))
+    traces.sort(key=lambda a: a[:, 0].min())
+    last, before = traces[-1], traces[-2]
+    t0 = last[:, 0].min()
+    out = {"ctas": int(last.shape[0]), "period_us": round(float(t0 - before[:, 0].min()) / 1e3, 2)}
+    for i, point in enumerate(TIMELINE_POINTS):
+        column = last[:, i]
+        if (column > 0).any():
+            v = (column[column > 0] - t0) / 1e3
+            out[point] = [round(float(np.percentile(v, q)), 1) for q in (0, 50, 90, 100)]
+    return out
 
 
 def run_single_quant(args, device):
@@ -575,6 +608,9 @@ def main():
                     help="skip the hot per-shape rows and the prefill rows (launch-list captures of the step itself)")
     ap.add_argument("--gemm", default=None, metavar="NAME:M[:SCHEDULE[:HIGH_FRACTION[:fused]]]",
                     help="profiling aid: run only this GEMM (e.g. gate_up:16) a few times on cold weights and exit")
+    ap.add_argument("--timeline", action="store_true",
+                    help="with --gemm: load the trace build of the library (build.py --trace) and add the per-CTA "
+                         "timeline of the last launch to the JSON line")
     ap.add_argument("--quant", default=None, metavar="act|silu:ROWS:K",
                     help="profiling aid: run only this quantiser launch a few times on cold inputs and exit")
     ap.add_argument("--clip", default=None, metavar="ROWS:K",
@@ -594,6 +630,11 @@ def main():
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if args.gemm:
+        if args.timeline:
+            trace_library = ROOT / "comp2029-hybridgemm_b200" / "lib" / "libhygemm_b200_trace.so"
+            if not trace_library.exists():
+                raise SystemExit(f"--timeline needs {trace_library} (python comp2029-hybridgemm_b200/build.py --trace)")
+            os.environ["HYGEMM_LIBRARY"] = str(trace_library)
         run_single_gemm(args, device)
         return
     if args.quant:

@@ -107,9 +107,27 @@ struct TcParams {
   float* workspace;
   int* counters;
   int* status;
+#ifdef HG_TRACE
+  unsigned long long* trace;   // 16 time stamps per CTA, see HG_STAMP
+#endif
 };
 
 enum : int { kErrProducer = 1, kErrMmaFull = 2, kErrMmaAcc = 3, kErrEpilogue = 4, kErrDrain = 5, kErrLoader = 6 };
+// Builds with -DHG_TRACE record, per CTA, the global timer at sixteen points of the kernel (hg_trace reads them
+// back; `bench.py --timeline` prints their distribution over the grid).  Slots: 0 entry, 1 set-up done, 2 dependency
+// wait released (TMA thread), 3 first full stage seen by issuer 0, 4-7 issuer 0's commit of its first four units,
+// 8/9, 10/11, 12/13 start and end of the first three epilogues (thread 64).  Ordinary builds compile none of it.
+#ifdef HG_TRACE
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define HG_STAMP(slot) do { if (p.trace) p.trace[blockIdx.x * 16 + (slot)] = global_timer_ns(); } while (0)
+#else
+#define HG_STAMP(slot) do { } while (0)
+#endif
+
 constexpr long long kWaitLimitCycles = 4000000000ll;  // about 2 s at the boost clock, per wait
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -294,6 +312,7 @@ __global__ void __launch_bounds__(FUSED ? kTcThreads : kTcThreads - kQuantThread
 hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant__ CUtensorMap map_high,
                       const __grid_constant__ CUtensorMap map_act, const __grid_constant__ CtaHeads heads) {
   pdl_trigger();  // the next kernel in the stream may start its own set-up
+  if (threadIdx.x == 0) HG_STAMP(0);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -357,6 +376,7 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = uint32_t(*tmem_slot);
+  if (threadIdx.x == 0) HG_STAMP(1);
 
   // TMEM columns: acc_slots accumulator slots of issuers x acc_cols columns, then per issuer kScaleSets
   // sets of (SFA, SFB), 4 columns each.
@@ -376,6 +396,7 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
       // Activations and their scales come from the previous kernel; the MXFP4 weight stream of the loader
       // warps does not and is already running.  (Fused mode: this thread only moves weights and their scales.)
       if (!FUSED) pdl_wait();
+      HG_STAMP(2);
       for (int u = unit_begin; u < unit_end && !error; ++u) {
         const WorkUnit wu = u == unit_begin ? first_unit : p.units[u];
         const int part = wu.tile >= p.tiles[0];
@@ -567,6 +588,7 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
           const int nkb = min(2, wu.kb_end - kb);
           const int stage = ring_slot;   // (ring + l) % stages, kept incrementally with its round parity
           if (!mbar_wait(full_bar(stage), ring_round, abort_flag)) { error = kErrMmaFull; break; }
+          if (q == 0 && issued == 0) HG_STAMP(3);
           // The MXFP4 rows were written through the generic proxy (cp.async); the tensor core reads
           // shared memory through the async proxy.
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -594,6 +616,7 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
         ring += unit_stages;
         // Every issuer reports, also one that had no stage in this unit (its accumulator is then skipped).
         if (!error) tc_commit(acc_full_bar(slot));
+        if (q == 0 && acc_it < 4) HG_STAMP(4 + acc_it);
       }
       // Let every MMA issued by this thread retire before TMEM is released.
       tc_commit(drain_bar);
@@ -621,6 +644,7 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
       const bool ok = mbar_wait(acc_full_bar(slot), uint32_t(acc_it / p.acc_slots) & 1u, abort_flag);
       if (!epilogue_all(ok)) { error = kErrEpilogue; break; }
       tc_fence_after();
+      if (threadIdx.x == 64 && acc_it < 3) HG_STAMP(8 + 2 * acc_it);
       const int token0 = wu.token_tile * p.n_tile;
       // Issuers that owned a stage of this unit (global stages ring .. ring + unit_stages - 1, by ring slot).
       const uint32_t unit_stages = uint32_t(wu.kb_end - wu.kb_begin + 1) >> 1;
@@ -700,6 +724,7 @@ hybrid_gemm_tc_kernel(const __grid_constant__ TcParams p, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty_bar(slot));
+      if (threadIdx.x == 64 && acc_it < 3) HG_STAMP(9 + 2 * acc_it);
 
       if (wu.nsplit > 1 && !p.external_reduce) {
         // Deterministic split-K fix-up: the last unit of the tile to arrive sums
@@ -1137,6 +1162,9 @@ struct TcGemm {
   int* d_counters = nullptr;
   int* d_status = nullptr;
   int* d_cut = nullptr;
+#ifdef HG_TRACE
+  unsigned long long* d_trace = nullptr;
+#endif
   // Tensor maps of recent operand pointers (the shape is fixed per handle): a serving loop alternates among
   // a few activation buffers and one weight pointer, so the driver call is paid once per pointer.
   struct CachedMap { const void* ptr = nullptr; CUtensorMap map; };
@@ -1192,6 +1220,10 @@ TcGemm* tc_create(const hg_problem& l, const hg_problem& h, int schedule, int dt
   check(cudaMalloc(&g->d_counters, sizeof(int) * std::max(1, plan.counters)), "cudaMalloc counters");
     check(cudaMalloc(&g->d_status, sizeof(int) * 4), "cudaMalloc status");
   check(cudaMalloc(&g->d_cut, sizeof(int) * std::max<size_t>(4, plan.cut_tiles.size())), "cudaMalloc cut list");
+#ifdef HG_TRACE
+  check(cudaMalloc(&g->d_trace, sizeof(unsigned long long) * 16 * size_t(plan.grid)), "trace buffer");
+  check(cudaMemsetAsync(g->d_trace, 0, sizeof(unsigned long long) * 16 * size_t(plan.grid), stream), "trace buffer");
+#endif
   if (!plan.cut_tiles.empty())
     check(cudaMemcpyAsync(g->d_cut, plan.cut_tiles.data(), sizeof(int) * plan.cut_tiles.size(), cudaMemcpyHostToDevice, stream), "upload cut list");
   check(cudaMemcpyAsync(g->d_units, plan.units.data(), sizeof(WorkUnit) * plan.units.size(), cudaMemcpyHostToDevice, stream), "upload units");
@@ -1276,6 +1308,9 @@ void tc_run(TcGemm* g, const hg_problem& l, const hg_problem& h, cudaStream_t st
   p.x_bf16 = x_dtype == HG_DTYPE_BF16;
   p.units = g->d_units; p.cta_begin = g->d_cta_begin;
   p.workspace = g->d_workspace; p.counters = g->d_counters; p.status = g->d_status;
+#ifdef HG_TRACE
+  p.trace = g->d_trace;
+#endif
   // Tensor maps by operand pointer.  A map that the launch does not use (no MXFP8 rows; activations
   // quantised in the kernel) is passed as zeros and never touched by the kernel.
   static const CUtensorMap no_map{};
@@ -1316,10 +1351,25 @@ void tc_run(TcGemm* g, const hg_problem& l, const hg_problem& h, cudaStream_t st
 void tc_destroy(TcGemm* g) {
   if (!g) return;
   cudaFree(g->d_units); cudaFree(g->d_cta_begin); cudaFree(g->d_workspace); cudaFree(g->d_counters); cudaFree(g->d_status); cudaFree(g->d_cut);
+#ifdef HG_TRACE
+  cudaFree(g->d_trace);
+#endif
   delete g;
 }
 
 const Plan& tc_plan(const TcGemm* g) { return g->plan; }
+
+int tc_trace(TcGemm* g, cudaStream_t stream, unsigned long long* out, int max_values) {
+#ifdef HG_TRACE
+  const int values = std::min(max_values, 16 * g->plan.grid);
+  check(cudaMemcpyAsync(out, g->d_trace, sizeof(unsigned long long) * size_t(values), cudaMemcpyDeviceToHost, stream), "trace read");
+  check(cudaStreamSynchronize(stream), "trace read");
+  return values;
+#else
+  (void)g; (void)stream; (void)out; (void)max_values;
+  throw std::runtime_error("hg_trace needs a library built with -DHG_TRACE");
+#endif
+}
 
 void tc_kernel_attributes(int* registers, int* local_bytes) {
   cudaFuncAttributes attr{};

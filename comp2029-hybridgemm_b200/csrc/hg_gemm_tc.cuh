@@ -61,6 +61,9 @@ void tc_run(TcGemm*, const hg_problem& l, const hg_problem& h, cudaStream_t stre
             int x_dtype = HG_DTYPE_BF16, const PartialTarget* partial = nullptr);
 void tc_destroy(TcGemm*);
 const Plan& tc_plan(const TcGemm*);
+// Per-CTA time stamps of the handle's last launch (16 per CTA, nanoseconds of the global timer; 0 = not reached).
+// Only in builds with -DHG_TRACE; other builds throw.
+int tc_trace(TcGemm*, cudaStream_t stream, unsigned long long* out, int max_values);
 void tc_kernel_attributes(int* registers, int* local_bytes);
 // Reads (and clears) the device status words: [0] error code of a bounded wait
 // that gave up, [1] K128 blocks issued to the tensor core, [2] work units stored.

@@ -143,6 +143,15 @@ int hg_status(void* handle, void* stream, int* status) {
   HG_CATCH
 }
 
+int hg_trace(void* handle, void* stream, unsigned long long* out, int max_values, int* values) {
+  HG_TRY
+  if (!handle || !out || !values || max_values <= 0) throw std::runtime_error("Invalid hg_trace arguments");
+  auto* runner = static_cast<hg::Runner*>(handle);
+  if (!runner->tc) throw std::runtime_error("hg_trace: the handle has no tensor-core GEMM");
+  *values = hg::tc_trace(runner->tc, static_cast<cudaStream_t>(stream), out, max_values);
+  HG_CATCH
+}
+
 int hg_plan(int rows_low, int rows_high, int tokens, int k, int sms, int schedule, int* header, int* units,
             int max_units) {
   HG_TRY

@@ -78,6 +78,7 @@ def library():
     lib.hg_status.argtypes = [vp, vp, C.POINTER(ci)]
     lib.hg_destroy.argtypes, lib.hg_destroy.restype = [vp], None
     lib.hg_plan.argtypes = [ci] * 6 + [C.POINTER(ci), C.POINTER(ci), ci]
+    lib.hg_trace.argtypes = [vp, vp, C.POINTER(C.c_uint64), ci, C.POINTER(ci)]
     lib.hg_run_static.argtypes = [ci, pp, pp, vp, ci]
     lib.hg_static_status.argtypes = [vp, C.POINTER(ci)]
     lib.hg_run_partial.argtypes = [vp, pp, pp, vp, ci, vp, C.c_int64, ci, vp, vp]

@@ -122,6 +122,12 @@ int hg_status(void* handle, void* stream, int* status);
  * kb_begin, kb_end, split, nsplit, ws_slot, counter. */
 int hg_plan(int rows_low, int rows_high, int tokens, int k, int sms, int schedule, int* header, int* units,
             int max_units);
+/* Diagnostic, only in a library built with -DHG_TRACE (build.py --trace; ordinary builds return -1 with an
+ * error): per-CTA time stamps of the handle's last tensor-core launch, 16 per CTA in nanoseconds of the GPU's
+ * global timer (0 = point not reached): entry, set-up done, dependency wait released, first full stage, the
+ * first four units' last commit, start and end of the first three epilogues.  *values = words written.
+ * Synchronises `stream`.  (No counterpart in the reference; `bench.py --timeline` prints the distribution.) */
+int hg_trace(void* handle, void* stream, unsigned long long* out, int max_values, int* values);
 
 /* Bytes of the fixed scratch array behind hg_run_static (held on every GPU that loads the library). */
 #define HG_STATIC_SCRATCH_BYTES (8u << 20)

@@ -52,6 +52,9 @@ def test_scale_size_and_argument_errors_without_gpu():
     assert lib.hg_create(0, 0, C.byref(empty), C.byref(empty), None, C.byref(handle)) == -1
     assert b"at least one weight row" in lib.hg_last_error()
     assert lib.hg_run(None, C.byref(empty), C.byref(empty), None, 0) == -1
+    count = C.c_int(0)
+    assert lib.hg_trace(None, None, (C.c_uint64 * 16)(), 16, C.byref(count)) == -1     # diagnostic entry point
+    assert lib.hg_last_error() == b"Invalid hg_trace arguments"
 
 
 def plan(lo, hi, tokens, k, schedule=0, sms=148):
